@@ -1,0 +1,104 @@
+"""ctypes binding of ``libmcsparse_b200.so`` (the C ABI in ``include/mcsparse_b200.h``).
+
+There is no fallback: if the shared library is missing or does not export a
+symbol, importing a kernel wrapper raises.  Build it with
+``python -m mcsparse_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmcsparse_b200.so"
+
+MCS_DTYPE_BF16 = 0
+MCS_DTYPE_FP16 = 1
+MCS_DTYPE_E4M3 = 2
+
+# Every symbol the header declares; the CPU test-suite checks this list against
+# the header and against the built library.
+EXPORTED_SYMBOLS = (
+    "mcs_version",
+    "mcs_built_for_sm",
+    "mcs_error_string",
+    "mcs_gather_attn_fwd",
+)
+
+
+class GatherAttnArgs(C.Structure):
+    """Mirror of ``mcs_gather_attn_args``."""
+
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("gi", C.c_void_p), ("gl", C.c_void_p),
+        ("residual", C.c_void_p), ("perm", C.c_void_p),
+        ("scale_qk_log2", C.c_void_p), ("scale_v", C.c_void_p), ("status", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("o_stride", C.c_int64 * 3), ("r_stride", C.c_int64 * 3),
+        ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
+        ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
+        ("softmax_scale", C.c_float),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the shared library once and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m mcsparse_b200.build` "
+            "(there is no CPU or PyTorch fallback for the kernels)")
+    L = C.CDLL(str(LIB_PATH))
+    L.mcs_version.restype = C.c_int
+    L.mcs_built_for_sm.restype = C.c_int
+    L.mcs_error_string.restype = C.c_char_p
+    L.mcs_error_string.argtypes = [C.c_int]
+    L.mcs_gather_attn_fwd.restype = C.c_int
+    L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
+    _lib = L
+    return L
+
+
+def error_string(code: int) -> str:
+    return lib().mcs_error_string(int(code)).decode()
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel reported a non-zero device status (an expired bounded wait)."""
+
+
+_status_words: dict = {}
+
+
+def status_word(device):
+    """Per-device int32 status word shared by all launches (zero = healthy)."""
+    import torch
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status_words[key] = t
+    return t
+
+
+def check_enabled() -> bool:
+    """``MCSPARSE_B200_CHECK=1`` makes every wrapper synchronise and read the status word."""
+    return os.environ.get("MCSPARSE_B200_CHECK", "0") == "1"
+
+
+def check_status(device, where: str = "") -> None:
+    """Synchronise and raise if any kernel on ``device`` reported an error."""
+    import torch
+    t = status_word(device)
+    torch.cuda.synchronize(t.device)
+    code = int(t.item())
+    if code != 0:
+        t.zero_()
+        raise KernelStatusError(f"mcsparse_b200 kernel status {code} ({where}): a bounded device-side wait expired")

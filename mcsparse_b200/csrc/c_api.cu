@@ -1,0 +1,80 @@
+// C ABI of the library: argument validation and dispatch to the kernels.
+// Nothing here synchronises, allocates or frees.
+#include "../../include/mcsparse_b200.h"
+
+#include <cmath>
+
+#include "kernels.cuh"
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int mcs_version(void) { return 1; }
+int mcs_built_for_sm(void) { return 100; }
+
+const char* mcs_error_string(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case MCS_ERR_NULL_POINTER: return "required pointer is null";
+    case MCS_ERR_BAD_SHAPE: return "invalid shape";
+    case MCS_ERR_BAD_HEAD_DIM: return "unsupported head dimension";
+    case MCS_ERR_BAD_DTYPE: return "unsupported element type";
+    case MCS_ERR_BAD_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+    case MCS_ERR_BAD_SCALE: return "softmax scale must be positive and finite";
+    case MCS_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case MCS_ERR_LAUNCH_FAILED: return "kernel launch failed";
+    case MCS_ERR_UNSUPPORTED: return "unsupported configuration";
+    case MCS_ERR_TOO_LARGE: return "size exceeds the supported maximum";
+    default: return "unknown error";
+  }
+}
+
+int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->out == nullptr ||
+      a->gi == nullptr || a->status == nullptr)
+    return MCS_ERR_NULL_POINTER;
+  if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return MCS_ERR_BAD_SHAPE;
+  if (a->gather_len < 128 || a->gather_len % 128 != 0) return MCS_ERR_BAD_SHAPE;
+  if (a->group_rows < 1 || a->group_rows > 128) return MCS_ERR_BAD_SHAPE;
+  if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16 && a->dtype != MCS_DTYPE_E4M3)
+    return MCS_ERR_BAD_DTYPE;
+  const int esize = a->dtype == MCS_DTYPE_E4M3 ? 1 : 2;
+  const int row_align = 16 / esize;  // elements per 16 bytes
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out) ||
+      (a->residual != nullptr && !aligned16(a->residual)))
+    return MCS_ERR_BAD_ALIGNMENT;
+  for (int i = 0; i < 3; ++i) {
+    if (a->q_stride[i] % row_align || a->k_stride[i] % row_align || a->v_stride[i] % row_align) return MCS_ERR_BAD_ALIGNMENT;
+    if (a->o_stride[i] % 8) return MCS_ERR_BAD_ALIGNMENT;
+    if (a->residual != nullptr && a->r_stride[i] % 8) return MCS_ERR_BAD_ALIGNMENT;
+  }
+  const long long groups = ((long long)a->Sq + a->group_rows - 1) / a->group_rows;
+  if ((long long)a->B * a->H * groups > 0x7fffffffLL) return MCS_ERR_TOO_LARGE;
+
+  mcs::GatherAttnParams p{};
+  p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out; p.lse = a->lse;
+  p.gi = a->gi; p.gl = a->gl; p.residual = a->residual; p.perm = a->perm;
+  p.scale_qk_log2 = a->scale_qk_log2; p.scale_v = a->scale_v; p.status = a->status;
+  for (int i = 0; i < 3; ++i) {
+    p.q_stride[i] = a->q_stride[i]; p.k_stride[i] = a->k_stride[i]; p.v_stride[i] = a->v_stride[i];
+    p.o_stride[i] = a->o_stride[i]; p.r_stride[i] = a->r_stride[i];
+  }
+  p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.H = a->H; p.D = a->D;
+  p.M = (int)groups; p.gather_len = a->gather_len; p.group_rows = a->group_rows;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (a->dtype == MCS_DTYPE_E4M3) {
+    return MCS_ERR_UNSUPPORTED;
+  }
+  if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;
+  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  return mcs::launch_gather_attn_16bit(p, a->dtype == MCS_DTYPE_FP16, s);
+}
+
+}  // extern "C"

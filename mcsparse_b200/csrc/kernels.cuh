@@ -1,0 +1,28 @@
+// Internal launch interfaces shared between the kernels and the C ABI layer.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace mcs {
+
+struct GatherAttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  const int32_t* gi;
+  const int32_t* gl;
+  const void* residual;
+  const int64_t* perm;
+  const float* scale_qk_log2;  // e4m3 only
+  const float* scale_v;        // e4m3 only
+  int* status;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], r_stride[3];
+  int B, Sq, Sk, H, D, M, gather_len, group_rows;
+  float scale_log2;  // softmax_scale * log2(e)
+};
+
+int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
+
+}  // namespace mcs
