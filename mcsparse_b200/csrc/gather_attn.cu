@@ -1,31 +1,43 @@
 // Gather-KV sparse flash-attention forward for sm_100a (bf16 / fp16).
 //
-// One CTA per (batch, head, query group).  A query group is up to 128 rows of
-// the (optionally permuted) query sequence that share one list of selected KV
-// token indices.  Per 128-token KV tile:
+// Persistent kernel, one CTA per SM.  A work item is one query group: up to 128
+// rows of the (optionally permuted) query sequence of one (batch, head) that
+// share one list of selected KV token indices.  CTAs walk the items round-robin
+// in (head-major, group-minor) order so that the groups in flight at any moment
+// read the K/V of one or two heads, which then stay resident in L2.
 //
-//   producer warps   gather the tile's K rows and V rows with 16-byte cp.async
-//                    (16 lanes cover one 256-byte row, so every warp request is
-//                    two fully used 256-byte segments) into 128-byte-swizzled
-//                    shared memory in the canonical tcgen05 operand layout;
-//   MMA warp         one thread issues S = Q K^T (tcgen05.mma, operands in shared
-//                    memory, accumulator in tensor memory) and O += P V (P read
-//                    from tensor memory, V as an MN-major shared-memory operand);
-//   softmax warps    thread r owns query row r == TMEM lane r: reads its S row
-//                    with tcgen05.ld, keeps the online-softmax state in
-//                    registers (log2 domain, lazy rescale of O), writes P back
-//                    into the S columns as packed 16-bit values.
+// Roles inside the CTA (416 threads = 13 warps, so that no SM sub-partition hosts more than
+// four warps and every thread can have 128 registers):
+//   warps 0-3   softmax stream A: columns 0-63 of every 128-token KV tile
+//   warps 4-7   softmax stream B: columns 64-127
+//               thread r of a stream owns query row r (= TMEM lane r).  Each
+//               stream keeps its own online-softmax state (row max, row sum)
+//               and its own output accumulator in tensor memory, so the two
+//               halves never exchange anything until the epilogue merges them.
+//   warps 8-11  producers: gather the tile's K rows and V rows with 16-byte
+//               cp.async (16 lanes cover one 256-byte row) into a 5-slot ring of
+//               128-byte-swizzled tiles in the canonical tcgen05 operand layout;
+//               completion is signalled by cp.async.mbarrier.arrive.  The row
+//               gather is the scarcest resource of the kernel (measured ceiling about
+//               38 B/clk/SM with four warps issuing), hence the deep ring.
+//   warp 12     MMA issuer (one thread): S = Q K^T into a double-buffered score
+//               tile, O_x += P_x V_x for both streams (P read from tensor memory,
+//               V as an MN-major shared-memory operand).
 //
-// Two CTAs are resident per SM (96 KB shared memory and 256 TMEM columns each),
-// so one CTA's softmax overlaps the other's tensor-core work.
+// Tensor memory (512 columns): score buffers S[0], S[1] (128 columns each; P of a
+// stream overwrites the first 32 columns of its half), O_A, O_B (128 columns each).
+// Because S is double-buffered the QK^T of tile g+1 is issued before the softmax
+// of tile g finishes, also across work items (Q is double-buffered in shared
+// memory), so the tensor pipe only waits when softmax falls behind.
 //
-// The epilogue normalises O, adds the cached dense-minus-sparse residual in fp32,
-// rounds once to the output type and scatters rows back to the original token
-// order when a permutation is given.
+// The epilogue merges the two streams (O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / l),
+// adds the cached dense-minus-sparse residual in fp32, rounds once to the output
+// type and scatters rows back to the original token order when a permutation is
+// given.
 //
-// Follows the math of the reference's Hopper kernel
+// Math follows the reference's Hopper kernel
 // (mcsparse/kernels/flash_mcsa/ops/flash_sparse_attn/cute/flash_fwd_sm90.py:1005-1340,
-// softmax.py:126-227) and the gather addressing of topk_gather_kv.py:351-445.
+// softmax.py:126-227); gather addressing follows topk_gather_kv.py:351-445.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -36,56 +48,92 @@ namespace mcs {
 
 namespace {
 
-constexpr int kTileN = 128;          // KV tokens per tile
-constexpr int kThreads = 288;        // 4 softmax warps + 4 producer warps + 1 MMA warp
-constexpr int kSoftmaxThreads = 128;
-constexpr int kProducerThreads = 128;
-constexpr int kMmaWarp = 8;
-constexpr uint32_t kTmemCols = 256;  // S: [0,128)  O: [128, 128+D)
-constexpr float kRescaleThreshold = 8.0f;  // log2 units; P stays <= 2^8
+constexpr int kTileN = 128;            // KV tokens per tile
+constexpr int kThreads = 416;          // 8 softmax warps + 4 producer warps + 1 MMA warp
+constexpr int kStreamThreads = 128;
+constexpr int kProducerWarps = 4;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kRowsPerProducerWarp = 128 / kProducerWarps;
+constexpr int kProducerWarp0 = 8;
+constexpr int kMmaWarp = 12;
+// All 13 warps run with the same 128-register budget (no setmaxnreg: with a partial fourth
+// warpgroup its hand-over never completed on this part).  The softmax loop is written as a
+// streaming pass over 16 score columns at a time so that it needs about half of that.
+constexpr int kRing = 5;               // K/V tile slots
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0;          // S[buf] at kColS + 128*buf
+constexpr uint32_t kColO = 256;        // O_A at 256, O_B at 384
+constexpr int kMaxDynSmem = 232448;    // 227 KB
 
-// mbarrier slots
-enum { BAR_Q_FULL = 0, BAR_K_FULL, BAR_V_FULL, BAR_K_EMPTY, BAR_V_EMPTY, BAR_S_FULL, BAR_P_READY, BAR_O_FULL,
-       BAR_DRAIN, BAR_COUNT };
+enum {
+  BAR_FULL = 0,                        // [kRing] producers -> MMA
+  BAR_EMPTY = BAR_FULL + kRing,        // [kRing] MMA -> producers
+  BAR_Q_FULL = BAR_EMPTY + kRing,      // [2]
+  BAR_Q_EMPTY = BAR_Q_FULL + 2,        // [2]
+  BAR_S_FULL = BAR_Q_EMPTY + 2,        // [2] score tile ready
+  BAR_P_READY = BAR_S_FULL + 2,        // [2 streams][2 bufs]
+  BAR_PV_DONE = BAR_P_READY + 4,       // [2] O stable after tile in buf
+  BAR_O_FULL = BAR_PV_DONE + 2,
+  BAR_O_EMPTY,
+  BAR_STATS,                           // both streams published their (max, sum) of the finished item
+  BAR_DRAIN,
+  BAR_COUNT
+};
 
 template <int D>
 struct Smem {
   static constexpr int kBlocks = D / 64;                 // 64-element (128-byte) column blocks
   static constexpr int kTileBytes = kBlocks * 16384;     // 128 rows x D x 2 bytes
-  static constexpr int kQ = 0;
-  static constexpr int kK = kTileBytes;
-  static constexpr int kV = 2 * kTileBytes;
-  static constexpr int kBars = 3 * kTileBytes;
-  static constexpr int kTmemSlot = kBars + BAR_COUNT * 8;
+  static constexpr int kQ = 0;                           // 2 buffers
+  static constexpr int kRingOff = 2 * kTileBytes;
+  static constexpr int kBars = kRingOff + kRing * kTileBytes;
+  static constexpr int kStats = kBars + BAR_COUNT * 8;   // float2 [2 streams][128]
+  static constexpr int kTmemSlot = kStats + 2 * 128 * 8;
   static constexpr int kTotal = kTmemSlot + 16;
-  static constexpr int kDynamic = kTotal + 1024;         // slack for 1024-byte alignment
+  static constexpr int kDynamic = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
 };
 
-// Byte offset of 16-byte chunk `c` of row `row` inside a swizzled operand tile.
-__device__ __forceinline__ uint32_t swz_off(int row, int c) {
-  return static_cast<uint32_t>((c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4));
-}
+#ifdef MCS_TRACE
+// Diagnostics build: per-role clock accumulators of CTA 0, written once at the end.
+// trace[role*16 + slot]; TR_BEGIN/TR_END bracket a region, TR_FLUSH stores the sums.
+#define TR_DECL long long tr_acc[12] = {0}; long long tr_t = 0; (void)tr_t
+#define TR_BEGIN() tr_t = clock64()
+#define TR_END(slot) do { const long long tr_n = clock64(); tr_acc[slot] += tr_n - tr_t; tr_t = tr_n; } while (0)
+#define TR_FLUSH(role, cond)                                                          \
+  do {                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && (cond))                              \
+      for (int tr_i = 0; tr_i < 12; ++tr_i) p.trace[(role) * 16 + tr_i] = tr_acc[tr_i]; \
+  } while (0)
+#else
+#define TR_DECL do { } while (0)
+#define TR_BEGIN() do { } while (0)
+#define TR_END(slot) do { } while (0)
+#define TR_FLUSH(role, cond) do { } while (0)
+#endif
 
-// One warp copies 32 rows of D 16-bit elements.  `row_ptr_of_lane` is the global
-// address of row (row0 + lane); rows with a null pointer are zero-filled.
+// One producer warp copies kRowsPerProducerWarp rows of D 16-bit elements into a swizzled
+// tile.  Lane (l % rows) holds the source row index of tile row (row0 + l); a negative
+// index zero-fills the row.  `lane_src` = table base + 16 * (this lane's chunk).
 template <int D>
-__device__ __forceinline__ void warp_gather_rows(uint32_t s_tile, int row0, const uint8_t* row_ptr_of_lane,
-                                                 const uint8_t* any_valid, int lane) {
+__device__ __forceinline__ void warp_gather_rows(uint32_t s_tile, int row0, int my_row_idx, const uint8_t* lane_src,
+                                                 size_t row_bytes, int lane) {
   constexpr int kChunks = D / 8;             // 16-byte chunks per row
   constexpr int kRowsPerInstr = 32 / kChunks;
   const int sub = lane / kChunks;
   const int c = lane % kChunks;
+  // row0 is a multiple of 8, so (row & 7) == (rl & 7); the chunk XOR splits into a per-lane
+  // part and a compile-time part
+  const uint32_t dst0 = s_tile + (c >> 3) * 16384 + (row0 + sub) * 128;
+  const uint32_t cs4 = static_cast<uint32_t>(((c & 7) ^ sub) << 4);
 #pragma unroll
-  for (int i = 0; i < 32 / kRowsPerInstr; ++i) {
+  for (int i = 0; i < kRowsPerProducerWarp / kRowsPerInstr; ++i) {
     const int rl = i * kRowsPerInstr + sub;
-    const unsigned long long p =
-        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(row_ptr_of_lane), rl);
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(p);
-    const uint32_t dst = s_tile + swz_off(row0 + rl, c);
-    if (src != nullptr) {
-      cp_async16(dst, src + c * 16);
+    const int id = __shfl_sync(0xffffffffu, my_row_idx, rl);
+    const uint32_t dst = dst0 + i * kRowsPerInstr * 128 + (cs4 ^ (((i * kRowsPerInstr) & 7) << 4));
+    if (id >= 0) {
+      cp_async16(dst, lane_src + (size_t)id * row_bytes);
     } else {
-      cp_async16_zfill(dst, any_valid, 0);
+      cp_async16_zfill(dst, lane_src, 0);
     }
   }
 }
@@ -105,42 +153,65 @@ __device__ __forceinline__ float2 unpack16(uint32_t u) {
   }
 }
 
+// Decoded work item.
+struct Item {
+  int b, h, bh, m, row_base, rows_valid, T;
+  const int32_t* gi;
+};
+
+__device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item) {
+  Item it;
+  it.m = item % p.M;
+  it.bh = item / p.M;
+  it.h = it.bh % p.H;
+  it.b = it.bh / p.H;
+  it.row_base = it.m * p.group_rows;
+  it.rows_valid = min(p.group_rows, p.Sq - it.row_base);
+  const int max_tiles = p.gather_len / kTileN;
+  it.T = max_tiles;
+  if (p.gl != nullptr) it.T = min(max(p.gl[item], 1), max_tiles);
+  it.gi = p.gi + (size_t)item * p.gather_len;
+  return it;
+}
+
 template <int D, bool kFp16>
-__global__ void __launch_bounds__(kThreads, 2) gather_attn_kernel(const GatherAttnParams p) {
+__global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAttnParams p) {
   using L = Smem<D>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t sQ = s_base + L::kQ, sK = s_base + L::kK, sV = s_base + L::kV;
   const uint32_t bars = s_base + L::kBars;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  float2* stats = reinterpret_cast<float2*>(smem + L::kStats);
   auto bar = [&](int i) { return bars + 8u * i; };
+  auto sQ = [&](int qb) { return s_base + L::kQ + qb * L::kTileBytes; };
+  auto sRing = [&](int slot) { return s_base + L::kRingOff + slot * L::kTileBytes; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_items = p.B * p.H * p.M;
 
-  // ---- work assignment: m fastest so that resident CTAs share one head's K/V in L2
-  const int M = p.M;
-  const int m = blockIdx.x % M;
-  const int bh = blockIdx.x / M;
-  const int h = bh % p.H;
-  const int b = bh / p.H;
-  const int row_base = m * p.group_rows;
-  const int rows_valid = min(p.group_rows, p.Sq - row_base);
-  const int max_tiles = p.gather_len / kTileN;
-  int T = max_tiles;
-  if (p.gl != nullptr) T = min(max(p.gl[(size_t)bh * M + m], 1), max_tiles);
-  const int32_t* gi = p.gi + ((size_t)bh * M + m) * p.gather_len;
+  if (static_cast<int>(smem - smem_raw) + L::kTotal > L::kDynamic) {
+    if (tid == 0) atomicCAS(p.status, 0, 90);  // shared-memory carve-up does not fit: refuse to run
+    return;
+  }
 
   // ---- setup
   if (tid == 0) {
-    mbar_init(bar(BAR_Q_FULL), kProducerThreads);
-    mbar_init(bar(BAR_K_FULL), kProducerThreads);
-    mbar_init(bar(BAR_V_FULL), kProducerThreads);
-    mbar_init(bar(BAR_K_EMPTY), 1);
-    mbar_init(bar(BAR_V_EMPTY), 1);
-    mbar_init(bar(BAR_S_FULL), 1);
-    mbar_init(bar(BAR_P_READY), kSoftmaxThreads);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar(BAR_FULL + i), kProducerThreads);
+      mbar_init(bar(BAR_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_Q_FULL + i), kProducerThreads);
+      mbar_init(bar(BAR_Q_EMPTY + i), 1);
+      mbar_init(bar(BAR_S_FULL + i), 1);
+      mbar_init(bar(BAR_P_READY + i), kStreamThreads);
+      mbar_init(bar(BAR_P_READY + 2 + i), kStreamThreads);
+      mbar_init(bar(BAR_PV_DONE + i), 1);
+    }
     mbar_init(bar(BAR_O_FULL), 1);
+    mbar_init(bar(BAR_O_EMPTY), 2 * kStreamThreads);
+    mbar_init(bar(BAR_STATS), 2 * kStreamThreads);
     mbar_init(bar(BAR_DRAIN), 1);
     mbar_fence_init();
   }
@@ -152,209 +223,476 @@ __global__ void __launch_bounds__(kThreads, 2) gather_attn_kernel(const GatherAt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem;          // fp32 scores, 128 columns; P (16-bit) reuses columns [0,64)
-  const uint32_t tO = tmem + 128;    // fp32 output accumulator, D columns
 
-  if (warp < 4) {
+  if (warp < 8) {
     // =====================================================================
-    // softmax / correction / epilogue: thread == query row == TMEM lane
+    // softmax streams: thread == query row == TMEM lane
     // =====================================================================
-    const uint32_t lane_addr = (static_cast<uint32_t>(warp) * 32u) << 16;
+    const int x = warp >> 2;                       // stream 0 (A) or 1 (B)
+    const int r_in = (warp & 3) * 32 + lane;       // row inside the group
+    const uint32_t lane_addr = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
+    const uint32_t tOx = tmem + kColO + x * 128 + lane_addr;
     const float scale_log2 = p.scale_log2;
-    float m_run = -INFINITY;   // running (possibly stale) row max, log2 domain
-    float l_run = 0.f;         // running row sum relative to m_run
+    // Lazy rescale: the running max is only raised (and O rescaled) when a tile's max exceeds
+    // it by more than kRescale log2 units, so P stays <= 2^kRescale: far inside the bf16 / fp32
+    // range (threshold 24); fp16 P needs 2^kRescale * 1 <= 65504 (threshold 12).
+    constexpr float kRescale = kFp16 ? 12.0f : 24.0f;
+    int g = 0;      // tiles processed by this CTA so far
+    int ic = 0;     // items processed by this CTA so far
     bool ok = true;
-#pragma unroll 1
-    for (int t = 0; t < T && ok; ++t) {
-      ok = mbar_wait(bar(BAR_S_FULL), t & 1, p.status, 10);
-      if (!ok) break;
-      tc_fence_after();
-      // pass 1: row max of this tile
-      float mx = -INFINITY;
+    TR_DECL;
+    TR_BEGIN();
+
+    // ---- epilogue of a finished item, for this thread's row and this stream's half of the output
+    // columns: O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / l + residual, rounded once to the output type and
+    // written to the row's original position.  It is deferred: the residual reads are issued while
+    // the item's last tile is being processed, and the rest runs after the first tile of the NEXT
+    // item, when the item's last P V has long completed, so the softmax threads never sit idle
+    // waiting for the tensor pipe, and never wait for a global load.
+    constexpr int kHalf = D / 2;                 // output columns handled by this stream
+    struct Epi {
+      uint8_t* out;          // this row's output + column offset, or null for a padding row
+      const uint8_t* res;    // residual row + column offset, or null
+      float* lse;            // stream A only, or null
+    };
+    Epi epi{nullptr, nullptr, nullptr};
+    uint4 resv[kHalf / 8];
+    auto epilogue_prepare = [&](const Item& it) {
+      // pointers of this row; issue the residual reads (they complete during the item's last tile)
+      epi = Epi{nullptr, nullptr, nullptr};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_addr + c * 32, r);
-        tmem_wait_ld();
+      for (int i = 0; i < kHalf / 8; ++i) resv[i] = make_uint4(0, 0, 0, 0);
+      if (r_in < it.rows_valid) {
+        const int row = it.row_base + r_in;                       // position in (permuted) query order
+        long long orow = row;
+        if (p.perm != nullptr) orow = p.perm[(size_t)it.bh * p.Sq + row];
+        epi.out = reinterpret_cast<uint8_t*>(p.out) +
+                  2 * ((size_t)it.b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)it.h * p.o_stride[2] +
+                       (size_t)x * kHalf);
+        if (x == 0 && p.lse != nullptr) epi.lse = p.lse + (size_t)it.bh * p.Sq + orow;
+        if (p.residual != nullptr) {
+          epi.res = reinterpret_cast<const uint8_t*>(p.residual) +
+                    2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1] + (size_t)row * p.r_stride[2] +
+                         (size_t)x * kHalf);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-      }
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      if (t == 0) {
-        m_run = m_new;
-      } else {
-        const bool need = (m_new - m_run) > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? ex2_approx(m_run - m_new) : 1.f;
-          if (need) m_run = m_new;
-          l_run *= alpha;
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + lane_addr + c * 32, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO + lane_addr + c * 32, r);
-          }
+          for (int i = 0; i < kHalf / 8; ++i) resv[i] = ld_nc_v4(epi.res + i * 16);
         }
       }
-      // pass 2: P = exp2(S*scale - m), row sum, write P as packed 16-bit values
-      const float neg_m = -m_run;
-      float lsum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_addr + c * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), scale_log2, neg_m));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, neg_m));
-          lsum += p0 + p1;
-          pk[i] = pack16<kFp16>(p0, p1);
-        }
-        tmem_st16(tS + lane_addr + c * 16, pk);
-      }
-      l_run += lsum;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(BAR_P_READY));
-    }
-    // ---- epilogue
-    if (ok) ok = mbar_wait(bar(BAR_O_FULL), 0, p.status, 11);
-    if (ok) {
+    };
+    auto epilogue_finish = [&](int eic) -> bool {
+      // eic: CTA-local index of the item being finished; its statistics were published by both streams
+      if (!mbar_wait(bar(BAR_O_FULL), eic & 1, p.status, 11)) return false;
+      if (!mbar_wait(bar(BAR_STATS), eic & 1, p.status, 14)) return false;
       tc_fence_after();
-      const int r_in = warp * 32 + lane;
-      const bool valid = r_in < rows_valid;
-      const int row = row_base + r_in;                      // position in (permuted) query order
-      long long orow = row;
-      if (valid && p.perm != nullptr) orow = p.perm[(size_t)bh * p.Sq + row];
-      const float inv_l = 1.f / l_run;
-      uint8_t* optr = reinterpret_cast<uint8_t*>(p.out) +
-                      2 * ((size_t)b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)h * p.o_stride[2]);
-      const uint8_t* rptr = nullptr;
-      if (p.residual != nullptr)
-        rptr = reinterpret_cast<const uint8_t*>(p.residual) +
-               2 * ((size_t)b * p.r_stride[0] + (size_t)h * p.r_stride[1] + (size_t)row * p.r_stride[2]);
+      const float2 sa = stats[r_in], sb = stats[128 + r_in];
+      const float m_all = fmaxf(sa.x, sb.x);
+      const float fa = ex2_approx(sa.x - m_all), fb = ex2_approx(sb.x - m_all);
+      const float l_all = sa.y * fa + sb.y * fb;
+      const float inv_l = 1.f / l_all;
+      const float wa = fa * inv_l, wb = fb * inv_l;
+      const uint32_t tOa = tmem + kColO + x * kHalf + lane_addr;
+      const uint32_t tOb = tmem + kColO + 128 + x * kHalf + lane_addr;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tO + lane_addr + c * 32, r);
+      for (int c = 0; c < kHalf / 16; ++c) {
+        uint32_t ra[16], rb[16];
+        tmem_ld16(tOa + c * 16, ra);
+        tmem_ld16(tOb + c * 16, rb);
         tmem_wait_ld();
-        if (valid) {
+        if (c == kHalf / 16 - 1) {
+          // all of this thread's reads of O and of the statistics are done
+          tc_fence_before();
+          mbar_arrive_relaxed(bar(BAR_O_EMPTY));   // relaxed: must not wait for the output stores in flight
+        }
+        if (epi.out != nullptr) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 res = make_uint4(0, 0, 0, 0);
-            if (rptr != nullptr) res = *reinterpret_cast<const uint4*>(rptr + c * 64 + q4 * 16);
+          for (int q4 = 0; q4 < 2; ++q4) {
+            const uint4 res = resv[c * 2 + q4];
             const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
             uint32_t ow[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 rr = unpack16<kFp16>(rw[j]);
-              const float o0 = fmaf(__uint_as_float(r[q4 * 8 + 2 * j]), inv_l, rr.x);
-              const float o1 = fmaf(__uint_as_float(r[q4 * 8 + 2 * j + 1]), inv_l, rr.y);
+              const int k = q4 * 8 + 2 * j;
+              const float o0 = fmaf(__uint_as_float(ra[k]), wa, fmaf(__uint_as_float(rb[k]), wb, rr.x));
+              const float o1 = fmaf(__uint_as_float(ra[k + 1]), wa, fmaf(__uint_as_float(rb[k + 1]), wb, rr.y));
               ow[j] = pack16<kFp16>(o0, o1);
             }
-            *reinterpret_cast<uint4*>(optr + c * 64 + q4 * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            *reinterpret_cast<uint4*>(epi.out + c * 32 + q4 * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           }
         }
       }
-      if (valid && p.lse != nullptr) {
-        // natural-log LSE of the scaled logits
-        p.lse[(size_t)bh * p.Sq + orow] = (m_run + lg2_approx(l_run)) * 0.6931471805599453f;
-      }
-    }
-    tc_fence_before();
-  } else if (warp < 8) {
-    // =====================================================================
-    // producers: gather Q once, then K/V tiles
-    // =====================================================================
-    const int pw = warp - 4;
-    const int row0 = pw * 32;
-    const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q);
-    const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + 2 * ((size_t)b * p.k_stride[0] + (size_t)h * p.k_stride[2]);
-    const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v) + 2 * ((size_t)b * p.v_stride[0] + (size_t)h * p.v_stride[2]);
-    const size_t k_row = 2 * (size_t)p.k_stride[1], v_row = 2 * (size_t)p.v_stride[1];
-    {
-      const int r_in = row0 + lane;
-      const uint8_t* qrow = nullptr;
-      if (r_in < rows_valid) {
-        long long src_row = row_base + r_in;
-        if (p.perm != nullptr) src_row = p.perm[(size_t)bh * p.Sq + src_row];
-        qrow = qb + 2 * ((size_t)b * p.q_stride[0] + (size_t)src_row * p.q_stride[1] + (size_t)h * p.q_stride[2]);
-      }
-      warp_gather_rows<D>(sQ, row0, qrow, qb, lane);
-      cp_async_commit();
-    }
-    int idx = min(max(gi[row0 + lane], 0), p.Sk - 1);
-    bool ok = true;
+      // natural-log LSE of the scaled logits
+      if (epi.lse != nullptr) *epi.lse = (m_all + lg2_approx(l_all)) * 0.6931471805599453f;
+      return true;
+    };
+
+    bool epi_pending = false;   // the previous item still needs its epilogue
 #pragma unroll 1
-    for (int t = 0; t < T; ++t) {
-      if (t > 0) {
-        ok = mbar_wait(bar(BAR_K_EMPTY), (t - 1) & 1, p.status, 20);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+      const Item it = decode_item(p, item);
+      float m_run = -INFINITY;   // running (possibly stale) row max, log2 domain
+      float l_run = 0.f;         // running row sum relative to m_run
+#pragma unroll 1
+      for (int t = 0; t < it.T; ++t, ++g) {
+        const int buf = g & 1;
+        TR_END(0);
+        ok = mbar_wait(bar(BAR_S_FULL + buf), (g >> 1) & 1, p.status, 10);
         if (!ok) break;
-      }
-      warp_gather_rows<D>(sK, row0, kb + (size_t)idx * k_row, kb, lane);
-      cp_async_commit();
-      if (t > 0) {
-        ok = mbar_wait(bar(BAR_V_EMPTY), (t - 1) & 1, p.status, 21);
+        tc_fence_after();
+        TR_END(1);   // wait S_FULL
+        const uint32_t tSx = tmem + kColS + buf * 128 + x * 64 + lane_addr;
+        // Streaming online softmax over this stream's 64 score columns, 32 at a time: chunk max,
+        // lazy raise of the running max (rare), exp2, row sum, pack, store P.  P chunk q (16 packed
+        // columns at 16q) only overwrites score columns that were already read (chunk q sits at 32q).
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint32_t sc[32];
+          tmem_ld32(tSx + q * 32, sc);
+          tmem_wait_ld();
+          TR_END(2);   // tmem ld
+          float mx0 = fmaxf(__uint_as_float(sc[0]), __uint_as_float(sc[1]));
+          float mx1 = fmaxf(__uint_as_float(sc[2]), __uint_as_float(sc[3]));
+          float mx2 = fmaxf(__uint_as_float(sc[4]), __uint_as_float(sc[5]));
+          float mx3 = fmaxf(__uint_as_float(sc[6]), __uint_as_float(sc[7]));
+#pragma unroll
+          for (int i = 8; i < 32; i += 8) {
+            mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])));
+            mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3])));
+            mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5])));
+            mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7])));
+          }
+          const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+          const bool need = (m_new - m_run) > kRescale;       // always true for the first chunk of an item
+          if (__any_sync(0xffffffffu, need)) {
+            // Raise the running max: everything accumulated relative to the old max is multiplied
+            // by alpha = 2^(old - new): the row sum, the P chunk of this tile written so far and,
+            // from the second tile on, the output accumulator (stable once the previous P V is done).
+            const float alpha = need ? ex2_approx(m_run - m_new) : 1.f;
+            if (need) m_run = m_new;
+            l_run *= alpha;
+            if (t > 0) {
+              ok = mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, p.status, 12);
+              if (!ok) break;
+              tc_fence_after();
+#pragma unroll 1
+              for (int c = 0; c < D / 8; ++c) {
+                uint32_t r[8];
+                tmem_ld8(tOx + c * 8, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                tmem_st8(tOx + c * 8, r);
+              }
+            }
+#pragma unroll 1
+            for (int c = 0; c < 2 * q; ++c) {
+              uint32_t r[8];
+              tmem_ld8(tSx + c * 8, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float2 f = unpack16<kFp16>(r[i]);
+                r[i] = pack16<kFp16>(f.x * alpha, f.y * alpha);
+              }
+              tmem_st8(tSx + c * 8, r);
+            }
+            TR_END(4);   // rescale (rare)
+          }
+          const float neg_m = -m_run;
+          float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+              const int e = h2 * 16 + 2 * i;
+              const float p0 = ex2_approx(fmaf(__uint_as_float(sc[e]), scale_log2, neg_m));
+              const float p1 = ex2_approx(fmaf(__uint_as_float(sc[e + 1]), scale_log2, neg_m));
+              const float p2 = ex2_approx(fmaf(__uint_as_float(sc[e + 2]), scale_log2, neg_m));
+              const float p3 = ex2_approx(fmaf(__uint_as_float(sc[e + 3]), scale_log2, neg_m));
+              ls0 += p0;
+              ls1 += p1;
+              ls2 += p2;
+              ls3 += p3;
+              pk[i] = pack16<kFp16>(p0, p1);
+              pk[i + 1] = pack16<kFp16>(p2, p3);
+            }
+            tmem_st8(tSx + q * 16 + h2 * 8, pk);
+          }
+          l_run += (ls0 + ls1) + (ls2 + ls3);
+        }
         if (!ok) break;
+        TR_END(5);   // streaming softmax
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive_relaxed(bar(BAR_P_READY + 2 * x + buf));
+        TR_END(6);   // st + arrive
+        if (t == 0 && epi_pending) {
+          // the previous item's last P V completed long ago: finish it now
+          ok = epilogue_finish(ic - 1);
+          epi_pending = false;
+          if (!ok) break;
+          TR_END(8);   // deferred epilogue
+        }
+        if (t == it.T - 1) {
+          // Last tile done: publish this stream's (max, sum) (the previous item's were consumed by
+          // the epilogue above) and issue the residual reads of this row.
+          // (every thread of both streams must have read the previous item's statistics: normally
+          // long true, the wait only matters for items of one or two tiles)
+          if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
+          if (!ok) break;
+          stats[x * 128 + r_in] = make_float2(m_run, l_run);
+          mbar_arrive(bar(BAR_STATS));
+          epilogue_prepare(it);
+          epi_pending = true;
+          TR_END(7);   // publish stats, issue residual reads
+        }
       }
-      warp_gather_rows<D>(sV, row0, vb + (size_t)idx * v_row, vb, lane);
-      cp_async_commit();
-      if (t + 1 < T) idx = min(max(gi[(t + 1) * kTileN + row0 + lane], 0), p.Sk - 1);
-      if (t == 0) {
-        cp_async_wait<2>();
-        fence_proxy_async_smem();
-        mbar_arrive(bar(BAR_Q_FULL));
-      }
-      cp_async_wait<1>();
-      fence_proxy_async_smem();
-      mbar_arrive(bar(BAR_K_FULL));
-      cp_async_wait<0>();
-      fence_proxy_async_smem();
-      mbar_arrive(bar(BAR_V_FULL));
+      if (!ok) break;
     }
-    cp_async_wait<0>();
+    if (ok && epi_pending) ok = epilogue_finish(ic - 1);
+    TR_FLUSH(x, lane == 0 && (warp & 3) == 0);
+    tc_fence_before();
+  } else if (warp < kMmaWarp) {
+    // =====================================================================
+    // producers: K/V/Q row gathers, and the epilogue of every finished item.
+    //
+    // These four warps own all global-memory traffic of the CTA.  The softmax warps never
+    // use the load/store unit in steady state, so they are never queued behind the hundreds
+    // of cp.async that are in flight.  Producer warp pw gathers tile rows 32*pw..+31 and, in
+    // the epilogue, owns TMEM lanes 32*pw..+31 (its own sub-partition): one query row per
+    // thread in both jobs.
+    // =====================================================================
+    const int pw = warp - kProducerWarp0;
+    const int row0 = pw * kRowsPerProducerWarp;
+    const int my_row = row0 + lane;                              // tile row / query row of this thread
+    const int chunk_off = (lane % (D / 8)) * 16;                 // this lane's 16-byte chunk inside a row
+    const size_t q_row = 2 * (size_t)p.q_stride[1], k_row = 2 * (size_t)p.k_stride[1], v_row = 2 * (size_t)p.v_stride[1];
+    int slot = 0, slot_phase = 0;   // ring position; the phase flips every wrap
+    bool wrapped = false;
+    bool ok = true;
+    TR_DECL;
+    TR_BEGIN();
+
+    auto enter_item = [&](int item, int ic) {
+      // called once per item when the K cursor reaches it: request Q, remember epilogue pointers,
+      // warm L2 for this item's residual and for the next item's indices
+      const Item it = decode_item(p, item);
+      const int qbuf = ic & 1;
+      int src_row = -1;
+      if (my_row < it.rows_valid) {
+        const int row = it.row_base + my_row;
+        src_row = row;
+        if (p.perm != nullptr) src_row = static_cast<int>(p.perm[(size_t)it.bh * p.Sq + row]);
+        if (p.residual != nullptr) {
+          const uint8_t* res_row = reinterpret_cast<const uint8_t*>(p.residual) +
+                                   2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1] + (size_t)row * p.r_stride[2]);
+          prefetch_l2(res_row);
+          if (D == 128) prefetch_l2(res_row + 128);
+        }
+      }
+      if (item + (int)gridDim.x < n_items) {
+        const uint8_t* gin = reinterpret_cast<const uint8_t*>(p.gi + (size_t)(item + gridDim.x) * p.gather_len);
+        const int bytes = p.gather_len * 4;
+        for (int off = (pw * 32 + lane) * 128; off < bytes; off += kProducerThreads * 128) prefetch_l2(gin + off);
+      }
+      if (ic >= 2) ok = ok && mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((ic >> 1) - 1) & 1, p.status, 22);
+      if (!ok) return;
+      const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
+                          2 * ((size_t)it.b * p.q_stride[0] + (size_t)it.h * p.q_stride[2]) + chunk_off;
+      warp_gather_rows<D>(sQ(qbuf), row0, src_row, qb, q_row, lane);
+      cp_async_arrive_noinc(bar(BAR_Q_FULL + qbuf));
+    };
+
+    auto load_tile = [&](const uint8_t* lane_src, size_t row_bytes, int idx) {
+      TR_END(0);
+      if (wrapped) ok = ok && mbar_wait(bar(BAR_EMPTY + slot), slot_phase ^ 1, p.status, 20);
+      if (!ok) return;
+      TR_END(1);   // wait for a free ring slot
+      // raw index, clamped only here: the global load issued one step earlier stays in flight until now
+      warp_gather_rows<D>(sRing(slot), row0, min(max(idx, 0), p.Sk - 1), lane_src, row_bytes, lane);
+      cp_async_arrive_noinc(bar(BAR_FULL + slot));
+      TR_END(2);   // issue the tile's cp.async
+      if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
+    };
+
+    // per-item constants of a cursor
+    struct Cur {
+      int item, ic, t, T;
+      const int32_t* gi;     // this thread's entry of tile 0
+      const uint8_t* kv;     // K or V base of (b, h) + chunk offset of this lane
+    };
+    auto set_item = [&](Cur& c, const void* tensor, const int64_t* stride) {
+      const Item it = decode_item(p, c.item);
+      c.T = it.T;
+      c.gi = it.gi + my_row;
+      c.kv = reinterpret_cast<const uint8_t*>(tensor) + 2 * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
+    };
+    auto load_idx = [&](const Cur& c) { return __ldg(c.gi + c.t * kTileN); };
+
+    // Fill order = consumption order of the MMA warp: K(0), then per tile g: K(g+1), V(g),
+    // where g+1 may belong to the next work item (its Q is requested just before its K(0)).
+    // The indices of the next K tile are fetched one step ahead of their use.
+    if (blockIdx.x < n_items) {
+      Cur kc{static_cast<int>(blockIdx.x), 0, 0, 0, nullptr, nullptr}, vc = kc;
+      set_item(kc, p.k, p.k_stride);
+      set_item(vc, p.v, p.v_stride);
+      enter_item(kc.item, kc.ic);
+      int idx_k = load_idx(kc);
+      load_tile(kc.kv, k_row, idx_k);
+      int idx_v = idx_k;
+      auto advance_k = [&]() {
+        if (++kc.t >= kc.T) {
+          kc.t = 0;
+          kc.item += gridDim.x;
+          ++kc.ic;
+          if (kc.item < n_items) set_item(kc, p.k, p.k_stride);
+        }
+      };
+      advance_k();
+      bool have_k = kc.item < n_items;
+      if (have_k) idx_k = load_idx(kc);
+#pragma unroll 1
+      while (ok) {
+        const int idx_cur = idx_k;
+        const bool had_k = have_k;
+        if (had_k) {
+          if (kc.t == 0) enter_item(kc.item, kc.ic);
+          if (!ok) break;
+          load_tile(kc.kv, k_row, idx_cur);
+          if (!ok) break;
+          advance_k();
+          have_k = kc.item < n_items;
+          if (have_k) idx_k = load_idx(kc);       // in flight while V(g) is issued
+        }
+        load_tile(vc.kv, v_row, idx_v);
+        if (!ok) break;
+        idx_v = idx_cur;                           // V(g+1) uses the indices of K(g+1)
+        if (++vc.t >= vc.T) {
+          if (!had_k) break;                       // last tile of the last item
+          vc.t = 0;
+          vc.item += gridDim.x;
+          ++vc.ic;
+          set_item(vc, p.v, p.v_stride);
+        }
+      }
+    }
+    cp_async_wait_all();
+    tc_fence_before();
+    TR_FLUSH(2, pw == 0 && lane == 0);
   } else {
     // =====================================================================
-    // MMA issuer: one thread
+    // MMA issuer: one thread.  tcgen05.mma issue blocks while the (shallow) MMA queue is
+    // full, so every instruction between two MMAs is exposed: descriptors are pre-built
+    // and ring positions are tracked incrementally.
     // =====================================================================
-    if (lane == 0) {
+    if (lane == 0 && blockIdx.x < n_items) {
       constexpr uint32_t kFmt = kFp16 ? 0u : 1u;
       constexpr uint32_t idesc_qk = mma_idesc(kFmt, kFmt, 0, 0, 128, kTileN);
       constexpr uint32_t idesc_pv = mma_idesc(kFmt, kFmt, 0, 1, 128, D);
-      bool ok = mbar_wait(bar(BAR_Q_FULL), 0, p.status, 30);
-#pragma unroll 1
-      for (int t = 0; t < T && ok; ++t) {
-        ok = mbar_wait(bar(BAR_K_FULL), t & 1, p.status, 31);
-        if (!ok) break;
+      // descriptor high word: stride byte offset 1024, version 1, 128-byte swizzle
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLboK = (16u >> 4) << 16;       // K-major operands (Q, K): LBO unused
+      constexpr uint32_t kLboV = (16384u >> 4) << 16;    // MN-major V: 16 KB between 64-element column blocks
+      auto desc = [&](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+      bool ok = true;
+      int slot = 0, slot_phase = 0;
+      TR_DECL;
+      TR_BEGIN();
+      auto next_slot = [&]() { if (++slot == kRing) { slot = 0; slot_phase ^= 1; } };
+
+      // QK^T of global tile gq (tile t of T of the CTA's ic-th item)
+      auto issue_qk = [&](int gq, int ic, int t, int T) -> bool {
+        const int qbuf = ic & 1;
+        TR_END(0);
+        if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) return false;
+        TR_END(10);  // wait Q full
+        if (!mbar_wait(bar(BAR_FULL + slot), slot_phase, p.status, 30)) return false;
+        TR_END(1);   // wait K (and Q) full
         fence_proxy_async_smem();
         tc_fence_after();
+        const uint32_t tS = tmem + kColS + (gq & 1) * 128;
+        const uint32_t qlo = ((sQ(qbuf) & 0x3FFFFu) >> 4) | kLboK;
+        const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboK;
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
-          const uint32_t koff = (j >> 2) * 16384 + (j & 3) * 32;
-          mma_f16_ss(tS, smem_desc_sw128(sQ + koff, 16, 1024), smem_desc_sw128(sK + koff, 16, 1024), idesc_qk,
-                     j > 0);
+          constexpr uint32_t kStep = 32 >> 4;   // 16 elements = 32 bytes inside the 128-byte swizzle span
+          const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * kStep;
+          mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
         }
-        tc_commit(bar(BAR_K_EMPTY));
-        tc_commit(bar(BAR_S_FULL));
-        ok = mbar_wait(bar(BAR_V_FULL), t & 1, p.status, 32);
-        if (!ok) break;
-        ok = mbar_wait(bar(BAR_P_READY), t & 1, p.status, 33);
-        if (!ok) break;
+        TR_END(2);   // issue QK MMAs
+        tc_commit(bar(BAR_EMPTY + slot));
+        tc_commit(bar(BAR_S_FULL + (gq & 1)));
+        if (t == T - 1) tc_commit(bar(BAR_Q_EMPTY + qbuf));
+        TR_END(3);   // QK commits
+        next_slot();
+        return true;
+      };
+      auto issue_pv = [&](int gp, int ic, int t, int T) -> bool {
+        TR_END(0);
+        if (!mbar_wait(bar(BAR_FULL + slot), slot_phase, p.status, 34)) return false;
+        TR_END(4);   // wait V full
+        if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) return false;
+        TR_END(5);   // wait O empty
+        const int buf = gp & 1;
+        const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
         fence_proxy_async_smem();
-        tc_fence_after();
 #pragma unroll
-        for (int j = 0; j < kTileN / 16; ++j) {
-          // A: 16 packed 16-bit values = 8 TMEM columns per k-step; B: 16 KV rows = 2048 bytes
-          mma_f16_ts(tO, tS + j * 8, smem_desc_sw128(sV + j * 2048, 16384, 1024), idesc_pv, (t > 0) || (j > 0));
+        for (int x = 0; x < 2; ++x) {
+          if (!mbar_wait(bar(BAR_P_READY + 2 * x + buf), (gp >> 1) & 1, p.status, 33)) return false;
+          TR_END(6 + x);   // wait P ready (stream x)
+          tc_fence_after();
+          const uint32_t tP = tmem + kColS + buf * 128 + x * 64;
+          const uint32_t tO = tmem + kColO + x * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // A: 16 packed 16-bit values = 8 TMEM columns per k-step; B: 16 KV rows = 2048 bytes
+            mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (j > 0));
+          }
+          TR_END(8);   // issue PV MMAs
         }
-        tc_commit(bar(BAR_V_EMPTY));
+        tc_commit(bar(BAR_EMPTY + slot));
+        tc_commit(bar(BAR_PV_DONE + buf));
         if (t == T - 1) tc_commit(bar(BAR_O_FULL));
+        TR_END(9);   // PV commits
+        next_slot();
+        return true;
+      };
+
+      int q_item = blockIdx.x, q_ic = 0, q_t = 0, q_T = decode_item(p, q_item).T, gq = 0;
+      int v_ic = 0, v_t = 0, v_T = q_T, gp = 0;
+      auto advance_q = [&]() {
+        ++gq;
+        if (++q_t >= q_T) {
+          q_t = 0;
+          q_item += gridDim.x;
+          ++q_ic;
+          if (q_item < n_items) q_T = decode_item(p, q_item).T;
+        }
+      };
+      ok = issue_qk(gq, q_ic, q_t, q_T);
+      advance_q();
+#pragma unroll 1
+      while (ok) {
+        const bool have_q = q_item < n_items;
+        const int next_T = q_T;
+        if (have_q) {
+          ok = issue_qk(gq, q_ic, q_t, q_T);
+          if (!ok) break;
+        }
+        ok = issue_pv(gp, v_ic, v_t, v_T);
+        if (!ok) break;
+        ++gp;
+        if (++v_t >= v_T) {
+          if (!have_q) break;
+          v_t = 0;
+          ++v_ic;
+          v_T = next_T;
+        }
+        if (have_q) advance_q();
       }
+      TR_END(0);
+      TR_FLUSH(3, true);
       if (!ok) {
         // error path: let outstanding MMAs retire before tensor memory is released
         tc_commit(bar(BAR_DRAIN));
@@ -372,14 +710,27 @@ __global__ void __launch_bounds__(kThreads, 2) gather_attn_kernel(const GatherAt
   }
 }
 
+int num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int D, bool kFp16>
 int launch(const GatherAttnParams& p, cudaStream_t stream) {
   using L = Smem<D>;
   auto kern = gather_attn_kernel<D, kFp16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return -8;
-  const long long grid = (long long)p.B * p.H * p.M;
-  kern<<<(unsigned)grid, kThreads, L::kDynamic, stream>>>(p);
+  const long long items = (long long)p.B * p.H * p.M;
+  const int grid = (int)(items < num_sms() ? items : num_sms());
+  kern<<<grid, kThreads, L::kDynamic, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

@@ -21,6 +21,7 @@ struct GatherAttnParams {
   int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], r_stride[3];
   int B, Sq, Sk, H, D, M, gather_len, group_rows;
   float scale_log2;  // softmax_scale * log2(e)
+  long long* trace;  // diagnostics builds only (MCS_TRACE): per-role event clocks of CTA 0
 };
 
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);

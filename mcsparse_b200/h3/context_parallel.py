@@ -1,0 +1,100 @@
+"""Ulysses context parallelism for the token-sparse attention path.
+
+Sequence-sharded activations (B, L/N, H, D) are resharded to head-sharded full-sequence
+tensors (B, L, H/N, D) with one all-to-all, the sparse attention runs on the local heads
+with rank-local metadata (indices, residual and permutation are per head, so no metadata
+ever crosses ranks), and one all-to-all brings the output back to (B, L/N, H, D).
+
+The reference delegates the two all-to-alls to diffusers'
+``_templated_context_parallel_attention`` and runs its kernel as the ``forward_op``
+(mcsparse/h3/context_parallel.py:154-231); ring / KV-rotation parallelism is rejected there
+(:212-218) and here, because sparse routing needs the whole KV sequence of a head.
+
+Semantics restated (standard Ulysses): sequence shards are concatenated in rank order;
+heads are split contiguously in rank order.  Received data lands in this rank's own HBM
+buffers and the kernels only ever read local memory.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class UlyssesReshard:
+    """Pre-allocated sequence<->head resharding for one attention layer shape.
+
+    ``seq_to_head`` issues all peer transfers of q, k and v as ONE grouped NCCL operation;
+    the received tensors are used in place (for B == 1 the receive buffer already is the
+    (1, L, H/N, D) tensor the attention kernel wants, so there is no unpack copy).
+    """
+
+    def __init__(self, group, seq_len: int, heads: int, head_dim: int, dtype, device, batch: int = 1):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if heads % self.world != 0:
+            raise ValueError(f"Ulysses needs heads ({heads}) divisible by the number of ranks ({self.world})")
+        if seq_len % self.world != 0:
+            raise ValueError(f"Ulysses needs sequence length ({seq_len}) divisible by the number of ranks ({self.world})")
+        self.B, self.L, self.H, self.D = batch, seq_len, heads, head_dim
+        self.Ls, self.Hl = seq_len // self.world, heads // self.world
+        N, B, Ls, Hl, D = self.world, batch, self.Ls, self.Hl, head_dim
+        mk = lambda: torch.empty(N, B, Ls, Hl, D, dtype=dtype, device=device)
+        self._send = [mk() for _ in range(3)]
+        self._recv = [mk() for _ in range(3)]
+        self._osend = mk() if B > 1 else None
+        self._orecv = mk()
+        self.kernels_per_step = 0
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _a2a(self, sends: Sequence[torch.Tensor], recvs: Sequence[torch.Tensor]) -> None:
+        if self.world == 1:
+            for s, r in zip(sends, recvs):
+                r.copy_(s)
+            return
+        if dist.get_backend(self.group) == "nccl":
+            ops = []
+            for s, r in zip(sends, recvs):
+                for peer in range(self.world):
+                    g = dist.get_global_rank(self.group, peer)
+                    ops.append(dist.P2POp(dist.isend, s[peer], g, self.group))
+                    ops.append(dist.P2POp(dist.irecv, r[peer], g, self.group))
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        else:
+            for s, r in zip(sends, recvs):
+                dist.all_to_all_single(r.view(-1), s.view(-1), group=self.group)
+
+    def _as_bshd(self, buf: torch.Tensor) -> torch.Tensor:
+        N, B, Ls, Hl, D = buf.shape
+        if B == 1:
+            return buf.view(1, N * Ls, Hl, D)
+        return buf.permute(1, 0, 2, 3, 4).reshape(B, N * Ls, Hl, D)
+
+    # -- API -------------------------------------------------------------------------------
+    def seq_to_head(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, ...]:
+        """(B, L/N, H, D) x3 -> (B, L, H/N, D) x3."""
+        N, B, Ls, Hl, D = self.world, self.B, self.Ls, self.Hl, self.D
+        for t, s in zip((q, k, v), self._send):
+            if tuple(t.shape) != (B, Ls, self.H, D):
+                raise ValueError(f"expected a sequence shard of shape {(B, Ls, self.H, D)}, got {tuple(t.shape)}")
+            s.copy_(t.view(B, Ls, N, Hl, D).permute(2, 0, 1, 3, 4))
+        self._a2a(self._send, self._recv)
+        return tuple(self._as_bshd(r) for r in self._recv)
+
+    def head_to_seq(self, o: torch.Tensor) -> torch.Tensor:
+        """(B, L, H/N, D) -> (B, L/N, H, D)."""
+        N, B, Ls, Hl, D = self.world, self.B, self.Ls, self.Hl, self.D
+        if tuple(o.shape) != (B, self.L, Hl, D):
+            raise ValueError(f"expected a head shard of shape {(B, self.L, Hl, D)}, got {tuple(o.shape)}")
+        if B == 1 and o.is_contiguous():
+            send = o.view(N, 1, Ls, Hl, D)
+        else:
+            send = self._osend if self._osend is not None else torch.empty_like(self._orecv)
+            send.copy_(o.reshape(B, N, Ls, Hl, D).permute(1, 0, 2, 3, 4))
+        self._a2a([send], [self._orecv])
+        # received block i holds heads [i*Hl, (i+1)*Hl) of this rank's tokens
+        return self._orecv.permute(1, 2, 0, 3, 4).reshape(B, Ls, self.H, D)
