@@ -99,6 +99,37 @@ typedef struct mcs_gather_attn_args {
 
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* args, void* stream);
 
+/*
+ * Anchor-step group mass: mass[b,h,m,j] = sum_{i in group m} exp(scale * q_i . k_j - lse_i), fp32.
+ *
+ * Replaces: mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-117
+ * (_token_probs_kernel_bf16 / _compute_token_probs_bf16_triton) as called from
+ * mcsparse/kernels/flash_mcsa/token_sparse.py:590-595 (_compute_token_probs).
+ * Differences: the result is fp32 (the reference rounds to bf16, which creates rank ties),
+ * and it is the plain sum unless `normalize` is set (then it is divided by the number of rows
+ * in the group, the reference's convention).  Groups are `group_rows` consecutive positions
+ * of the query order given by `perm` (identity if NULL); `lse` is indexed by position in that
+ * order, as the dense pass that produced it ran on the permuted queries
+ * (token_sparse.py:1058, 1151).
+ */
+typedef struct mcs_group_mass_args {
+  const void* q;        /* (B, Lq, H, D) element strides q_stride[0..2], bf16/fp16 */
+  const void* k;        /* (B, Lk, H, D) */
+  const float* lse;     /* (B*H, Lq) contiguous fp32, natural log, softmax scale included */
+  const int64_t* perm;  /* (B*H, Lq) contiguous int64, or NULL */
+  float* mass;          /* (B*H, M, Lk) contiguous fp32, M = ceil(Lq / group_rows) */
+  int32_t* status;
+  int64_t q_stride[3];
+  int64_t k_stride[3];
+  int32_t B, H, Lq, Lk, D;
+  int32_t group_rows;   /* 1..128 */
+  int32_t dtype;        /* MCS_DTYPE_BF16 or MCS_DTYPE_FP16 */
+  int32_t normalize;    /* 0: sum, 1: divide by rows in group */
+  float softmax_scale;  /* > 0 */
+} mcs_group_mass_args;
+
+int mcs_group_mass(const mcs_group_mass_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

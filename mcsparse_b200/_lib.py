@@ -24,6 +24,7 @@ EXPORTED_SYMBOLS = (
     "mcs_built_for_sm",
     "mcs_error_string",
     "mcs_gather_attn_fwd",
+    "mcs_group_mass",
 )
 
 
@@ -39,6 +40,19 @@ class GatherAttnArgs(C.Structure):
         ("o_stride", C.c_int64 * 3), ("r_stride", C.c_int64 * 3),
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
         ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
+        ("softmax_scale", C.c_float),
+    ]
+
+
+class GroupMassArgs(C.Structure):
+    """Mirror of ``mcs_group_mass_args``."""
+
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("lse", C.c_void_p), ("perm", C.c_void_p),
+        ("mass", C.c_void_p), ("status", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
+        ("B", C.c_int32), ("H", C.c_int32), ("Lq", C.c_int32), ("Lk", C.c_int32), ("D", C.c_int32),
+        ("group_rows", C.c_int32), ("dtype", C.c_int32), ("normalize", C.c_int32),
         ("softmax_scale", C.c_float),
     ]
 
@@ -62,8 +76,21 @@ def lib() -> C.CDLL:
     L.mcs_error_string.argtypes = [C.c_int]
     L.mcs_gather_attn_fwd.restype = C.c_int
     L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
+    L.mcs_group_mass.restype = C.c_int
+    L.mcs_group_mass.argtypes = [C.POINTER(GroupMassArgs), C.c_void_p]
     _lib = L
     return L
+
+
+def launch(fn_name: str, args, device, where: str) -> None:
+    """Call an entry point on the current torch stream of ``device``; raise on an argument error."""
+    import torch
+    stream = torch.cuda.current_stream(device).cuda_stream
+    rc = getattr(lib(), fn_name)(args, stream)
+    if rc != 0:
+        raise RuntimeError(f"{where}: {error_string(rc)} (code {rc})")
+    if check_enabled():
+        check_status(device, where)
 
 
 def error_string(code: int) -> str:

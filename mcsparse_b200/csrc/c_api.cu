@@ -85,4 +85,27 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
   return mcs::launch_gather_attn_16bit(p, a->dtype == MCS_DTYPE_FP16, s);
 }
 
+int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->lse == nullptr || a->mass == nullptr || a->status == nullptr)
+    return MCS_ERR_NULL_POINTER;
+  if (a->B < 1 || a->H < 1 || a->Lq < 1 || a->Lk < 1) return MCS_ERR_BAD_SHAPE;
+  if (a->group_rows < 1 || a->group_rows > 128) return MCS_ERR_BAD_SHAPE;
+  if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
+  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;
+  if (!aligned16(a->q) || !aligned16(a->k)) return MCS_ERR_BAD_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (a->q_stride[i] % 8 || a->k_stride[i] % 8) return MCS_ERR_BAD_ALIGNMENT;
+  const long long groups = ((long long)a->Lq + a->group_rows - 1) / a->group_rows;
+  if ((long long)a->B * a->H * groups > 0x7fffffffLL) return MCS_ERR_TOO_LARGE;
+  mcs::GroupMassParams p{};
+  p.q = a->q; p.k = a->k; p.lse = a->lse; p.perm = a->perm; p.mass = a->mass; p.status = a->status;
+  for (int i = 0; i < 3; ++i) { p.q_stride[i] = a->q_stride[i]; p.k_stride[i] = a->k_stride[i]; }
+  p.B = a->B; p.H = a->H; p.Lq = a->Lq; p.Lk = a->Lk; p.D = a->D; p.M = (int)groups;
+  p.group_rows = a->group_rows; p.normalize = a->normalize;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.inv_scale = 1.0f / a->softmax_scale;
+  return mcs::launch_group_mass(p, a->dtype == MCS_DTYPE_FP16, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -1,0 +1,289 @@
+// Anchor-step group mass for sm_100a:
+//
+//   mass[b,h,m,j] = sum_{i in query group m} exp(scale * q_i . k_j - lse_i)        (fp32)
+//
+// i.e. the exact attention probability mass that query group m puts on key token j, given
+// the log-sum-exp of every query row from a dense attention pass.  Optionally divided by
+// the number of rows in the group (the reference's "mean" convention).
+//
+// Restates the reference's Triton kernel
+// (mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-89), with an fp32 result instead
+// of one rounded to bf16.
+//
+// One CTA per (batch*head, group).  The 128 query rows of the group stay resident in shared
+// memory; the CTA streams all key tiles of the head.  The product is computed TRANSPOSED,
+// S^T = K_tile Q^T, so that a TMEM lane is a key token and the sum over the group's queries
+// runs along the columns inside one thread: no cross-thread reduction at all.
+//
+// "- lse_i" is folded into the MMA: the contraction is extended by one 16-wide k-step whose K
+// columns are (1, 1, 1, 0, ...) and whose Q columns are (-hi, -mid, -lo, 0, ...), a three-term
+// bf16 split of lse_i / scale, exact to fp32 precision.  The tensor core then delivers
+// q_i . k_j - lse_i / scale and each element costs one multiply, one ex2 and one add.
+// The kernel is bound by the ex2 throughput of the SFU (16 per clock per SM).
+//
+// Roles: warps 0-3 exponentiate and sum (thread = key token), warp 4 issues the MMAs,
+// warps 5-8 stream the key tiles with cp.async into a 3-slot ring.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace mcs {
+
+namespace {
+
+constexpr int kTile = 128;
+constexpr int kThreads = 288;
+constexpr int kExpThreads = 128;
+constexpr int kProducerThreads = 128;
+constexpr int kMmaWarp = 4;
+constexpr int kRing = 3;
+constexpr uint32_t kTmemCols = 256;   // two score buffers of 128 columns
+
+enum { BAR_FULL = 0, BAR_EMPTY = BAR_FULL + kRing, BAR_Q_FULL = BAR_EMPTY + kRing, BAR_S_FULL, BAR_S_FREE = BAR_S_FULL + 2,
+       BAR_DRAIN = BAR_S_FREE + 2, BAR_COUNT };
+
+template <int D>
+struct Smem {
+  static constexpr int kBlocks = D / 64;
+  static constexpr int kTileBytes = kBlocks * 16384;
+  static constexpr int kQ = 0;                              // group's query rows (B operand)
+  static constexpr int kQx = kTileBytes;                    // extra k-step of Q: 128 rows x 128 B (first 32 B used)
+  static constexpr int kKx = kQx + 16384;                   // extra k-step of K: constant (1,1,1,0...)
+  static constexpr int kRingOff = kKx + 16384;
+  static constexpr int kBars = kRingOff + kRing * kTileBytes;
+  static constexpr int kTmemSlot = kBars + BAR_COUNT * 8;
+  static constexpr int kTotal = kTmemSlot + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+__device__ __forceinline__ uint32_t swz(int row, int c) {   // 16-byte chunk c of row, 128-byte swizzle
+  return static_cast<uint32_t>((c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+
+template <int D, bool kFp16>
+__global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMassParams p) {
+  using L = Smem<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bars = s_base + L::kBars;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  auto bar = [&](int i) { return bars + 8u * i; };
+  auto sRing = [&](int slot) { return s_base + L::kRingOff + slot * L::kTileBytes; };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int m = blockIdx.x % p.M;
+  const int bh = blockIdx.x / p.M;
+  const int h = bh % p.H, b = bh / p.H;
+  const int row_base = m * p.group_rows;
+  const int rows_valid = min(p.group_rows, p.Lq - row_base);
+  const int n_tiles = (p.Lk + kTile - 1) / kTile;
+
+  if (tid == 0) {
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar(BAR_FULL + i), kProducerThreads);
+      mbar_init(bar(BAR_EMPTY + i), 1);
+    }
+    mbar_init(bar(BAR_Q_FULL), 2 * kProducerThreads);   // per thread: its cp.async rows + its plain stores
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_S_FULL + i), 1);
+      mbar_init(bar(BAR_S_FREE + i), kExpThreads);
+    }
+    mbar_init(bar(BAR_DRAIN), 1);
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < 4) {
+    // ===================================================================== exp + column sum
+    const int j_in = warp * 32 + lane;                 // key token inside the tile == TMEM lane
+    const uint32_t lane_addr = (static_cast<uint32_t>(warp) * 32u) << 16;
+    const float c = p.scale_log2;
+    const float norm = p.normalize ? 1.f / static_cast<float>(rows_valid) : 1.f;
+    float* out = p.mass + ((size_t)bh * p.M + m) * p.Lk;
+    bool ok = true;
+#pragma unroll 1
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int buf = t & 1;
+      ok = mbar_wait(bar(BAR_S_FULL + buf), (t >> 1) & 1, p.status, 40);
+      if (!ok) break;
+      tc_fence_after();
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t r[32];
+        tmem_ld32(tmem + buf * 128 + q * 32 + lane_addr, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          a0 += ex2_approx(__uint_as_float(r[i]) * c);
+          a1 += ex2_approx(__uint_as_float(r[i + 1]) * c);
+          a2 += ex2_approx(__uint_as_float(r[i + 2]) * c);
+          a3 += ex2_approx(__uint_as_float(r[i + 3]) * c);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_relaxed(bar(BAR_S_FREE + buf));
+      const int j = t * kTile + j_in;
+      if (j < p.Lk) out[j] = ((a0 + a1) + (a2 + a3)) * norm;
+    }
+    tc_fence_before();
+  } else if (warp == kMmaWarp) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kFmt = kFp16 ? 0u : 1u;
+      constexpr uint32_t idesc = mma_idesc(kFmt, kFmt, 0, 0, 128, 128);
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLbo = (16u >> 4) << 16;
+      auto desc = [&](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+      const uint32_t qlo = (((s_base + L::kQ) & 0x3FFFFu) >> 4) | kLbo;
+      const uint32_t qxlo = (((s_base + L::kQx) & 0x3FFFFu) >> 4) | kLbo;
+      const uint32_t kxlo = (((s_base + L::kKx) & 0x3FFFFu) >> 4) | kLbo;
+      bool ok = mbar_wait(bar(BAR_Q_FULL), 0, p.status, 41);
+      int slot = 0, phase = 0;
+#pragma unroll 1
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int buf = t & 1;
+        if (t >= 2) ok = mbar_wait(bar(BAR_S_FREE + buf), ((t >> 1) - 1) & 1, p.status, 42);
+        ok = ok && mbar_wait(bar(BAR_FULL + slot), phase, p.status, 43);
+        if (!ok) break;
+        fence_proxy_async_smem();
+        tc_fence_after();
+        const uint32_t tS = tmem + buf * 128;
+        const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLbo;
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+          const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
+          mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);     // A = K tile, B = Q group
+        }
+        mma_f16_ss(tS, desc(kxlo), desc(qxlo), idesc, 1);                       // extra k-step: - lse / scale
+        tc_commit(bar(BAR_EMPTY + slot));
+        tc_commit(bar(BAR_S_FULL + buf));
+        if (++slot == kRing) { slot = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        tc_commit(bar(BAR_DRAIN));
+        mbar_wait_quiet(bar(BAR_DRAIN), 0, 1 << 20);
+      }
+    }
+    __syncwarp();
+    tc_fence_before();
+  } else {
+    // ===================================================================== producers
+    const int pw = warp - 5;
+    const int ptid = pw * 32 + lane;                    // 0..127: also the row this thread prepares
+    const int row0 = pw * 32;
+    constexpr int kChunks = D / 8;
+    constexpr int kRowsPerInstr = 32 / kChunks;
+    const int sub = lane / kChunks, cch = lane % kChunks;
+    // ---- constant extra K block, extra Q block, Q rows
+    {
+      // K extra: every row (1, 1, 1, 0, ...); Q extra: (-hi, -mid, -lo, 0, ...) of lse / scale
+      const uint32_t one = kFp16 ? 0x3C00u : 0x3F80u;
+      uint8_t* kx = smem + L::kKx;
+      uint8_t* qx = smem + L::kQx;
+      const int r = ptid;
+      uint4 kv0 = make_uint4(one | (one << 16), one, 0, 0);
+      float x = 3.0e38f;                                 // padding rows: exp(-huge) = 0
+      if (kFp16) x = 60000.f;
+      if (r < rows_valid) x = p.lse[(size_t)bh * p.Lq + row_base + r] * p.inv_scale;
+      uint32_t w0, w1;
+      if (kFp16) {
+        const __half hi = __float2half_rn(x);
+        const float r1 = x - __half2float(hi);
+        const __half mid = __float2half_rn(r1);
+        const __half lo = __float2half_rn(r1 - __half2float(mid));
+        w0 = (uint32_t)__half_as_ushort(__hneg(hi)) | ((uint32_t)__half_as_ushort(__hneg(mid)) << 16);
+        w1 = (uint32_t)__half_as_ushort(__hneg(lo));
+      } else {
+        const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+        const float r1 = x - __bfloat162float(hi);
+        const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+        w0 = (uint32_t)__bfloat16_as_ushort(__hneg(hi)) | ((uint32_t)__bfloat16_as_ushort(__hneg(mid)) << 16);
+        w1 = (uint32_t)__bfloat16_as_ushort(__hneg(lo));
+      }
+      // chunks 0 and 1 of the row carry the 16 columns of the k-step; the rest of the 128-byte row is unused
+      *reinterpret_cast<uint4*>(kx + swz(r, 0)) = kv0;
+      *reinterpret_cast<uint4*>(kx + swz(r, 1)) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(qx + swz(r, 0)) = make_uint4(w0, w1, 0, 0);
+      *reinterpret_cast<uint4*>(qx + swz(r, 1)) = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+      mbar_arrive(bar(BAR_Q_FULL));                      // release: the plain stores above
+      // Q rows (through the permutation if given)
+      int src = -1;
+      if (r < rows_valid) {
+        src = row_base + r;
+        if (p.perm != nullptr) src = static_cast<int>(p.perm[(size_t)bh * p.Lq + src]);
+      }
+      const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) + 2 * ((size_t)b * p.q_stride[0] + (size_t)h * p.q_stride[2]) + cch * 16;
+      const size_t q_row = 2 * (size_t)p.q_stride[1];
+#pragma unroll
+      for (int i = 0; i < 32 / kRowsPerInstr; ++i) {
+        const int rl = i * kRowsPerInstr + sub;
+        const int id = __shfl_sync(0xffffffffu, src, rl);
+        const uint32_t dst = s_base + L::kQ + swz(row0 + rl, cch);
+        if (id >= 0) cp_async16(dst, qb + (size_t)id * q_row);
+        else cp_async16_zfill(dst, qb, 0);
+      }
+      cp_async_arrive_noinc(bar(BAR_Q_FULL));
+    }
+    // ---- key tiles: contiguous rows t*128 .. t*128+127 of this head
+    const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + 2 * ((size_t)b * p.k_stride[0] + (size_t)h * p.k_stride[2]) + cch * 16;
+    const size_t k_row = 2 * (size_t)p.k_stride[1];
+    int slot = 0, phase = 0;
+    bool wrapped = false, ok = true;
+#pragma unroll 1
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      if (wrapped) ok = mbar_wait(bar(BAR_EMPTY + slot), phase ^ 1, p.status, 44);
+      if (!ok) break;
+      const uint32_t dst0 = sRing(slot);
+#pragma unroll
+      for (int i = 0; i < 32 / kRowsPerInstr; ++i) {
+        const int rl = row0 + i * kRowsPerInstr + sub;
+        const int krow = t * kTile + rl;
+        const uint32_t dst = dst0 + swz(rl, cch);
+        if (krow < p.Lk) cp_async16(dst, kb + (size_t)krow * k_row);
+        else cp_async16_zfill(dst, kb, 0);
+      }
+      cp_async_arrive_noinc(bar(BAR_FULL + slot));
+      if (++slot == kRing) { slot = 0; phase ^= 1; wrapped = true; }
+    }
+    cp_async_wait_all();
+  }
+
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int D, bool kFp16>
+int launch(const GroupMassParams& p, cudaStream_t stream) {
+  using L = Smem<D>;
+  auto kern = group_mass_kernel<D, kFp16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return -8;
+  const long long grid = (long long)p.B * p.H * p.M;
+  kern<<<(unsigned)grid, kThreads, L::kDynamic, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+}  // namespace
+
+int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream) {
+  if (p.D == 128) return fp16 ? launch<128, true>(p, stream) : launch<128, false>(p, stream);
+  if (p.D == 64) return fp16 ? launch<64, true>(p, stream) : launch<64, false>(p, stream);
+  return -3;
+}
+
+}  // namespace mcs

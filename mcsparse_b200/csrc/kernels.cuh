@@ -24,6 +24,20 @@ struct GatherAttnParams {
   long long* trace;  // diagnostics builds only (MCS_TRACE): per-role event clocks of CTA 0
 };
 
+struct GroupMassParams {
+  const void* q;        // (B, Lq, H, D) strided
+  const void* k;        // (B, Lk, H, D) strided
+  const float* lse;     // (B*H, Lq) in group (permuted) order
+  const int64_t* perm;  // (B*H, Lq) or null
+  float* mass;          // (B*H, M, Lk)
+  int* status;
+  int64_t q_stride[3], k_stride[3];
+  int B, H, Lq, Lk, D, M, group_rows, normalize;
+  float scale_log2;     // scale * log2(e)
+  float inv_scale;      // 1 / scale
+};
+
+int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 
 }  // namespace mcs
