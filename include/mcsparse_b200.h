@@ -130,6 +130,19 @@ typedef struct mcs_group_mass_args {
 
 int mcs_group_mass(const mcs_group_mass_args* args, void* stream);
 
+/*
+ * Exact top-k token selection with forced sink tokens.
+ *
+ * Replaces: mcsparse/kernels/flash_mcsa/token_sparse.py:755-945 (_select_topk_tokens, topk mode:
+ * sink masking :788-803, torch.topk :825-840, sink merge and 128-alignment :902-945).
+ * For each of `rows` score rows of length L (a row = one query group of one head) writes, in
+ * ascending order, the n_sink sink indices plus the (k_total - n_sink) non-sink indices with the
+ * highest fp32 score; ties go to the lowest index.  Requirements: n_sink <= 64, sinks distinct
+ * and in [0, L), n_sink <= k_total <= L.  The result is a pure function of the fp32 scores.
+ */
+int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink,
+                    int64_t rows, int32_t L, int32_t k_total, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

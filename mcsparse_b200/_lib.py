@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "mcs_error_string",
     "mcs_gather_attn_fwd",
     "mcs_group_mass",
+    "mcs_topk_select",
 )
 
 
@@ -78,6 +79,9 @@ def lib() -> C.CDLL:
     L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
     L.mcs_group_mass.restype = C.c_int
     L.mcs_group_mass.argtypes = [C.POINTER(GroupMassArgs), C.c_void_p]
+    L.mcs_topk_select.restype = C.c_int
+    L.mcs_topk_select.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                  C.c_void_p]
     _lib = L
     return L
 

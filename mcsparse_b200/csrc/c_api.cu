@@ -108,4 +108,13 @@ int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {
   return mcs::launch_group_mass(p, a->dtype == MCS_DTYPE_FP16, static_cast<cudaStream_t>(stream));
 }
 
+int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink, int64_t rows,
+                    int32_t L, int32_t k_total, void* stream) {
+  if (scores == nullptr || out == nullptr || (n_sink > 0 && sinks == nullptr)) return MCS_ERR_NULL_POINTER;
+  if (rows < 0 || L < 1 || n_sink < 0 || n_sink > 64 || k_total < n_sink || k_total > L) return MCS_ERR_BAD_SHAPE;
+  if (rows == 0) return 0;
+  mcs::TopkParams p{scores, out, sinks, (long long)rows, L, k_total, n_sink};
+  return mcs::launch_topk_select(p, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -37,6 +37,15 @@ struct GroupMassParams {
   float inv_scale;      // 1 / scale
 };
 
+struct TopkParams {
+  const float* scores;   // (rows, L)
+  int32_t* out;          // (rows, k_total) ascending
+  const int32_t* sinks;  // n_sink distinct indices in [0, L)
+  long long rows;
+  int L, k_total, n_sink;
+};
+
+int launch_topk_select(const TopkParams& p, cudaStream_t stream);
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 

@@ -78,3 +78,80 @@ def group_mass(q: torch.Tensor, k: torch.Tensor, lse: torch.Tensor, group_rows: 
 def _compute_token_probs(q, k, lse, BLKQ, scale):
     """Reference-compatible wrapper (token_sparse.py:590-595): mean over the block's rows, in q.dtype."""
     return group_mass(q, k, lse, group_rows=BLKQ, scale=scale, normalize=True).to(q.dtype)
+
+
+def _sink_indices(sink_ranges, L_K: int):
+    """Sorted distinct key positions covered by half-open ``sink_ranges`` (token_sparse.py:788-798)."""
+    idx = set()
+    for start, end in (sink_ranges or []):
+        idx.update(range(max(0, int(start)), min(int(end), L_K)))
+    return sorted(idx)
+
+
+def select_topk_with_sinks(scores: torch.Tensor, k_total: int, sink_ranges=None,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exact selection: the sink tokens plus the ``k_total - n_sink`` highest-scoring other tokens.
+
+    scores: (..., L) fp32 CUDA tensor (one row per query group).  Ties go to the lowest index and the
+    result is ascending int32 of shape (..., k_total): a pure function of the fp32 scores.
+    """
+    if scores.dtype != torch.float32:
+        raise TypeError("scores must be float32 (rank on the fp32 mass, not on a rounded copy)")
+    if not scores.is_cuda:
+        raise RuntimeError("scores must be a CUDA tensor")
+    L = scores.shape[-1]
+    sinks = _sink_indices(sink_ranges, L)
+    if len(sinks) > 64:
+        raise ValueError("at most 64 sink tokens are supported")
+    if not (len(sinks) <= k_total <= L):
+        raise ValueError(f"k_total must be in [n_sink={len(sinks)}, L={L}], got {k_total}")
+    scores = scores.contiguous()
+    rows = scores.numel() // L
+    shape = tuple(scores.shape[:-1]) + (k_total,)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.int32, device=scores.device)
+    elif tuple(out.shape) != shape or out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous int32 tensor of shape {shape}")
+    sink_t = torch.tensor(sinks, dtype=torch.int32, device=scores.device) if sinks else None
+    stream = torch.cuda.current_stream(scores.device).cuda_stream
+    rc = _lib.lib().mcs_topk_select(scores.data_ptr(), out.data_ptr(),
+                                    None if sink_t is None else sink_t.data_ptr(), len(sinks), rows, L,
+                                    int(k_total), stream)
+    if rc != 0:
+        raise RuntimeError(f"select_topk_with_sinks: {_lib.error_string(rc)} (code {rc})")
+    if _lib.check_enabled():
+        _lib.check_status(scores.device, "select_topk_with_sinks")
+    return out
+
+
+def _select_topk_tokens(token_probs, topk_ratio, tile_n=128, ds_k=1, orig_L_K=None,
+                        selection_mode='topk', topp=None, sink_ranges=None):
+    """Reference-shaped selection (token_sparse.py:755-945), ``topk`` mode, scalar ratio, ds_k == 1.
+
+    Budget arithmetic as in the reference: ``k_sel = min(L_K, align_up(max(1, int(ratio * L_K)), tile_n))``;
+    with sinks the list ``[sinks, top-k_sel]`` is cut to a whole number of tiles and tile counts are
+    returned, without sinks the counts are None.  Where the reference drops an arbitrary subset of an
+    unsorted top-k, this drops the lowest-ranked entries, and indices come back ascending.
+    Returns ``(gather_indices (B,H,M,gather_len) int32, gather_kv_lengths (B,H,M) int32 | None)``.
+    """
+    if selection_mode != 'topk':
+        raise NotImplementedError(f"selection_mode={selection_mode!r}: only 'topk' runs on this path")
+    if ds_k != 1:
+        raise NotImplementedError("key downsampling (ds_k > 1) is not part of this path")
+    if isinstance(topk_ratio, torch.Tensor):
+        raise NotImplementedError("adaptive per-head budgets are not part of this path")
+    B, H, M, L_K = token_probs.shape
+    n = max(1, int(topk_ratio * L_K))
+    k_sel = min(((n + tile_n - 1) // tile_n) * tile_n, L_K)
+    sinks = _sink_indices(sink_ranges, L_K)
+    scores = token_probs.float()
+    if not sinks:
+        gl = k_sel if k_sel % tile_n == 0 else max(tile_n, (k_sel // tile_n) * tile_n)
+        return select_topk_with_sinks(scores, min(gl, L_K)), None
+    total = k_sel + len(sinks)
+    cap = max(tile_n, min(((L_K + tile_n - 1) // tile_n) * tile_n, (total // tile_n) * tile_n))
+    count = min(max(min(((total + tile_n - 1) // tile_n) * tile_n, total), tile_n), cap)
+    count = min(count, L_K)
+    gi = select_topk_with_sinks(scores, count, sink_ranges)
+    lengths = torch.full((B, H, M), count // tile_n, dtype=torch.int32, device=token_probs.device)
+    return gi, lengths
