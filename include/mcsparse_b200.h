@@ -143,6 +143,53 @@ int mcs_group_mass(const mcs_group_mass_args* args, void* stream);
 int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink,
                     int64_t rows, int32_t L, int32_t k_total, void* stream);
 
+/*
+ * Fast PDDP query grouping: per (batch*head) permutation that puts similar rows into aligned
+ * blocks of C rows by recursive principal-direction bisection.
+ *
+ * Replaces: mcsparse/kernels/flash_mcsa/pca_group.py:141-243 (pca_group_perm), as called from
+ * mcsparse/kernels/flash_mcsa/token_sparse.py:254-293 (TokenSparseCache.get_or_make_perm).
+ * x: (BH, N, D) bf16/fp16, element strides x_stride_bh / x_stride_row, rows contiguous,
+ * D in {64, 128}.  perm_out: (BH, N) int64, x[b, perm[b, i]] is the i-th reordered row.
+ * start_vectors: the power-iteration start vectors, level-major: for level l a
+ * (BH * nodes_l, D) fp32 block (row b * nodes_l + node), mcs_pddp_start_vector_rows() rows in
+ * total.  The reference draws them from a generator on the tensor's device (:184-185, :224); host
+ * and device generators differ, so they are an input here.
+ * Optional dumps for checking: proj_levels (levels, BH, N) fp32 = projection of the row at every
+ * position of the order entering the level; perm_levels (levels + 1, BH, N) int32 = the order
+ * entering every level and the final one.  Given the fp32 projections the new order is their
+ * stable ascending sort inside every node: a pure function of those values.
+ * workspace: mcs_pddp_workspace_bytes(BH, N, C) bytes of device memory (0 = unsupported shape).
+ */
+typedef struct mcs_pddp_args {
+  const void* x;
+  const float* start_vectors;
+  int64_t* perm_out;
+  float* proj_levels;    /* or NULL */
+  int32_t* perm_levels;  /* or NULL */
+  void* workspace;
+  int32_t* status;
+  int64_t x_stride_bh, x_stride_row;
+  int64_t workspace_bytes;
+  int32_t BH, N, D, C, pow_iters;
+  int32_t dtype;         /* MCS_DTYPE_BF16 or MCS_DTYPE_FP16 */
+} mcs_pddp_args;
+
+int64_t mcs_pddp_workspace_bytes(int32_t BH, int32_t N, int32_t C);
+int64_t mcs_pddp_start_vector_rows(int32_t BH, int32_t N, int32_t C);
+int32_t mcs_pddp_levels(int32_t N, int32_t C);
+int mcs_pddp_perm(const mcs_pddp_args* args, void* stream);
+
+/*
+ * Row permutation of a (BH, L, D) tensor, 16-byte aligned rows of row_bytes bytes, byte strides.
+ * apply : out[b, i] = x[b, perm[b, i]]   replaces mcsparse/kernels/flash_mcsa/pca_group.py:40-42, 52-55
+ * invert: out[b, perm[b, i]] = x[b, i]   replaces pca_group.py:45-49, 58-61 (no argsort needed)
+ */
+int mcs_perm_apply(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes,
+                   int64_t x_bh_bytes, int64_t x_row_bytes, int64_t o_bh_bytes, int64_t o_row_bytes, void* stream);
+int mcs_perm_invert(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes,
+                    int64_t x_bh_bytes, int64_t x_row_bytes, int64_t o_bh_bytes, int64_t o_row_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,6 +26,12 @@ EXPORTED_SYMBOLS = (
     "mcs_gather_attn_fwd",
     "mcs_group_mass",
     "mcs_topk_select",
+    "mcs_pddp_workspace_bytes",
+    "mcs_pddp_start_vector_rows",
+    "mcs_pddp_levels",
+    "mcs_pddp_perm",
+    "mcs_perm_apply",
+    "mcs_perm_invert",
 )
 
 
@@ -58,6 +64,19 @@ class GroupMassArgs(C.Structure):
     ]
 
 
+class PddpArgs(C.Structure):
+    """Mirror of ``mcs_pddp_args``."""
+
+    _fields_ = [
+        ("x", C.c_void_p), ("start_vectors", C.c_void_p), ("perm_out", C.c_void_p),
+        ("proj_levels", C.c_void_p), ("perm_levels", C.c_void_p), ("workspace", C.c_void_p),
+        ("status", C.c_void_p),
+        ("x_stride_bh", C.c_int64), ("x_stride_row", C.c_int64), ("workspace_bytes", C.c_int64),
+        ("BH", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("C", C.c_int32), ("pow_iters", C.c_int32),
+        ("dtype", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -82,6 +101,18 @@ def lib() -> C.CDLL:
     L.mcs_topk_select.restype = C.c_int
     L.mcs_topk_select.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                   C.c_void_p]
+    L.mcs_pddp_workspace_bytes.restype = C.c_int64
+    L.mcs_pddp_workspace_bytes.argtypes = [C.c_int32] * 3
+    L.mcs_pddp_start_vector_rows.restype = C.c_int64
+    L.mcs_pddp_start_vector_rows.argtypes = [C.c_int32] * 3
+    L.mcs_pddp_levels.restype = C.c_int32
+    L.mcs_pddp_levels.argtypes = [C.c_int32] * 2
+    L.mcs_pddp_perm.restype = C.c_int
+    L.mcs_pddp_perm.argtypes = [C.POINTER(PddpArgs), C.c_void_p]
+    for fn in (L.mcs_perm_apply, L.mcs_perm_invert):
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                       C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
     _lib = L
     return L
 

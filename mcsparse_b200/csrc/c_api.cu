@@ -117,4 +117,49 @@ int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int
   return mcs::launch_topk_select(p, static_cast<cudaStream_t>(stream));
 }
 
+int64_t mcs_pddp_workspace_bytes(int32_t BH, int32_t N, int32_t C) { return (int64_t)mcs::pddp_workspace_bytes(BH, N, C); }
+int64_t mcs_pddp_start_vector_rows(int32_t BH, int32_t N, int32_t C) {
+  if (BH < 1 || N < 1 || C < 1) return 0;
+  return mcs::pddp_start_vector_rows(BH, N, C);
+}
+int32_t mcs_pddp_levels(int32_t N, int32_t C) { return (N < 1 || C < 1) ? 0 : mcs::pddp_levels(N, C); }
+
+int mcs_pddp_perm(const mcs_pddp_args* a, void* stream) {
+  if (a == nullptr || a->x == nullptr || a->perm_out == nullptr || a->workspace == nullptr || a->status == nullptr)
+    return MCS_ERR_NULL_POINTER;
+  if (a->BH < 1 || a->N < 1 || a->C < 1 || a->pow_iters < 0) return MCS_ERR_BAD_SHAPE;
+  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
+  if (!aligned16(a->x) || a->x_stride_bh % 8 || a->x_stride_row % 8) return MCS_ERR_BAD_ALIGNMENT;
+  const size_t need = mcs::pddp_workspace_bytes(a->BH, a->N, a->C);
+  if (need == 0) return MCS_ERR_TOO_LARGE;
+  if ((int64_t)need > a->workspace_bytes) return MCS_ERR_WORKSPACE_TOO_SMALL;
+  if (a->start_vectors == nullptr && mcs::pddp_levels(a->N, a->C) > 0) return MCS_ERR_NULL_POINTER;
+  mcs::PddpArgs p{};
+  p.x = a->x; p.x_stride_bh = a->x_stride_bh; p.x_stride_row = a->x_stride_row;
+  p.BH = a->BH; p.N = a->N; p.D = a->D; p.C = a->C; p.pow_iters = a->pow_iters; p.fp16 = a->dtype == MCS_DTYPE_FP16;
+  p.start_vectors = a->start_vectors; p.perm_out = reinterpret_cast<long long*>(a->perm_out);
+  p.proj_levels = a->proj_levels; p.perm_levels = a->perm_levels;
+  p.workspace = a->workspace; p.workspace_bytes = (size_t)a->workspace_bytes; p.status = a->status;
+  return mcs::launch_pddp(p, static_cast<cudaStream_t>(stream));
+}
+
+static int perm_rows(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes, int64_t x_bh,
+                     int64_t x_row, int64_t o_bh, int64_t o_row, bool invert, void* stream) {
+  if (x == nullptr || out == nullptr || perm == nullptr) return MCS_ERR_NULL_POINTER;
+  if (BH < 1 || L < 1 || row_bytes < 16) return MCS_ERR_BAD_SHAPE;
+  if (row_bytes % 16 || x_bh % 16 || x_row % 16 || o_bh % 16 || o_row % 16 || !aligned16(x) || !aligned16(out))
+    return MCS_ERR_BAD_ALIGNMENT;
+  return mcs::launch_perm_rows(x, out, reinterpret_cast<const long long*>(perm), BH, L, row_bytes, x_bh, x_row, o_bh, o_row, invert,
+                               static_cast<cudaStream_t>(stream));
+}
+int mcs_perm_apply(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes, int64_t x_bh,
+                   int64_t x_row, int64_t o_bh, int64_t o_row, void* stream) {
+  return perm_rows(x, out, perm, BH, L, row_bytes, x_bh, x_row, o_bh, o_row, false, stream);
+}
+int mcs_perm_invert(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes, int64_t x_bh,
+                    int64_t x_row, int64_t o_bh, int64_t o_row, void* stream) {
+  return perm_rows(x, out, perm, BH, L, row_bytes, x_bh, x_row, o_bh, o_row, true, stream);
+}
+
 }  // extern "C"

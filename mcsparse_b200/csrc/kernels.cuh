@@ -37,6 +37,34 @@ struct GroupMassParams {
   float inv_scale;      // 1 / scale
 };
 
+struct PddpParams {
+  const void* x;
+  long long x_stride_bh, x_stride_row;   // elements
+  int N, D, BH, pow_iters;
+  int* tables; int table_stride; int max_items;
+  float* partial;                        // [BH][max_items][128*128 + 128]
+  float* dir; int dir_nodes;             // [BH][dir_nodes][128]
+  unsigned long long* keys; size_t key_stride;
+  int* status;
+};
+struct PddpArgs {
+  const void* x; long long x_stride_bh, x_stride_row;
+  int BH, N, D, C, pow_iters; bool fp16;
+  const float* start_vectors;            // all levels, level-major: (BH * nodes_l, D) each
+  long long* perm_out;                   // (BH, N)
+  float* proj_levels;                    // optional (levels, BH, N)
+  int* perm_levels;                      // optional (levels + 1, BH, N)
+  void* workspace; size_t workspace_bytes;
+  int* status;
+};
+size_t pddp_workspace_bytes(int BH, int N, int C);
+long long pddp_start_vector_rows(int BH, int N, int C);
+int pddp_levels(int N, int C);
+int launch_pddp(const PddpArgs& a, cudaStream_t stream);
+
+int launch_perm_rows(const void* x, void* out, const long long* perm, int BH, int L, int row_bytes, long long x_bh,
+                     long long x_row, long long o_bh, long long o_row, bool invert, cudaStream_t stream);
+
 struct TopkParams {
   const float* scores;   // (rows, L)
   int32_t* out;          // (rows, k_total) ascending
