@@ -1,0 +1,58 @@
+"""CPU (gloo, world_size 2) tests of the Ulysses resharding: sharded == unsharded, error cases on the host."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, B, L, H, D, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mcsparse_b200.h3.context_parallel import UlyssesReshard
+        g = torch.Generator().manual_seed(0)
+        full = [torch.randn(B, L, H, D, generator=g) for _ in range(3)]         # same on every rank
+        Ls, Hl = L // world, H // world
+        shard = [t[:, rank * Ls:(rank + 1) * Ls].contiguous() for t in full]
+        r = UlyssesReshard(dist.group.WORLD, L, H, D, torch.float32, "cpu", batch=B)
+        qh, kh, vh = r.seq_to_head(*shard)
+        ok = all(torch.equal(a, t[:, :, rank * Hl:(rank + 1) * Hl]) for a, t in zip((qh, kh, vh), full))
+        # "attention" stand-in that mixes the whole sequence of a head: reverse along the sequence
+        o = qh.flip(1).contiguous()
+        back = r.head_to_seq(o)
+        expect = full[0].flip(1)[:, rank * Ls:(rank + 1) * Ls]
+        ok = ok and torch.equal(back, expect)
+        try:
+            UlyssesReshard(dist.group.WORLD, L, H + 1, D, torch.float32, "cpu")
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_ulysses_reshard_roundtrip_gloo(B):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, B, 16, 4, 8, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok in res), res
