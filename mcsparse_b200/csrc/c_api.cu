@@ -77,7 +77,10 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
 #endif
 
   if (a->dtype == MCS_DTYPE_E4M3) {
-    return MCS_ERR_UNSUPPORTED;
+    if (a->scale_qk_log2 == nullptr || a->scale_v == nullptr) return MCS_ERR_NULL_POINTER;
+    if (a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+    if (a->group_rows != 128) return MCS_ERR_BAD_SHAPE;
+    return mcs::launch_gather_attn_e4m3(p, s);
   }
   if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;
   if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;

@@ -1,4 +1,4 @@
-// Gather-KV sparse flash-attention forward for sm_100a (bf16 / fp16).
+// Gather-KV sparse flash-attention forward for sm_100a (bf16 / fp16 / FP8-e4m3 inputs).
 //
 // Persistent kernel, one CTA per SM.  A work item is one query group: up to 128
 // rows of the (optionally permuted) query sequence of one (batch, head) that
@@ -80,10 +80,10 @@ enum {
   BAR_COUNT
 };
 
-template <int D>
+template <int RB>     // RB = bytes per Q/K/V row (head_dim * element size)
 struct Smem {
-  static constexpr int kBlocks = D / 64;                 // 64-element (128-byte) column blocks
-  static constexpr int kTileBytes = kBlocks * 16384;     // 128 rows x D x 2 bytes
+  static constexpr int kBlocks = RB / 128;               // 128-byte column blocks
+  static constexpr int kTileBytes = kBlocks * 16384;     // 128 rows x RB bytes
   static constexpr int kQ = 0;                           // 2 buffers
   static constexpr int kRingOff = 2 * kTileBytes;
   static constexpr int kBars = kRingOff + kRing * kTileBytes;
@@ -114,10 +114,10 @@ struct Smem {
 // One producer warp copies kRowsPerProducerWarp rows of D 16-bit elements into a swizzled
 // tile.  Lane (l % rows) holds the source row index of tile row (row0 + l); a negative
 // index zero-fills the row.  `lane_src` = table base + 16 * (this lane's chunk).
-template <int D>
+template <int RB>
 __device__ __forceinline__ void warp_gather_rows(uint32_t s_tile, int row0, int my_row_idx, const uint8_t* lane_src,
                                                  size_t row_bytes, int lane) {
-  constexpr int kChunks = D / 8;             // 16-byte chunks per row
+  constexpr int kChunks = RB / 16;           // 16-byte chunks per row
   constexpr int kRowsPerInstr = 32 / kChunks;
   const int sub = lane / kChunks;
   const int c = lane % kChunks;
@@ -174,9 +174,18 @@ __device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item)
   return it;
 }
 
-template <int D, bool kFp16>
+// kType: 0 = bf16, 1 = fp16, 2 = e4m3 (Q/K/V 8-bit, P quantised to e4m3, fp32 accumulation, bf16 out).
+// FP8 follows the reference's contract (mcsparse/.../cute/interface.py:358-373, flash_fwd_sm90_fp8.py:
+// 145-241): logits = (q8 . k8) * scale_qk_log2[b,h,m] in the log2 domain, O * scale_v[b,h]; V is used
+// as it lies in memory (MN-major MMA operand), so neither the Hopper kernel's in-smem transpose nor
+// its d-column pre-permutation exists here.
+template <int D, int kType>
 __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAttnParams p) {
-  using L = Smem<D>;
+  constexpr bool kFp16 = kType == 1;
+  constexpr bool kFp8 = kType == 2;
+  constexpr int kEs = kFp8 ? 1 : 2;              // bytes per Q/K/V element
+  constexpr int RB = D * kEs;
+  using L = Smem<RB>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
@@ -232,11 +241,15 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     const int r_in = (warp & 3) * 32 + lane;       // row inside the group
     const uint32_t lane_addr = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
     const uint32_t tOx = tmem + kColO + x * 128 + lane_addr;
-    const float scale_log2 = p.scale_log2;
+    float scale_log2 = p.scale_log2;
     // Lazy rescale: the running max is only raised (and O rescaled) when a tile's max exceeds
-    // it by more than kRescale log2 units, so P stays <= 2^kRescale: far inside the bf16 / fp32
-    // range (threshold 24); fp16 P needs 2^kRescale * 1 <= 65504 (threshold 12).
-    constexpr float kRescale = kFp16 ? 12.0f : 24.0f;
+    // it by more than kRescale log2 units, so P stays <= 2^(kRescale + kBias): far inside the
+    // bf16 / fp32 range (threshold 24); fp16 P needs <= 65504 (threshold 12); e4m3 P must stay
+    // <= 448, and its 3-bit mantissa / 2^-9 floor want the row maximum well above 1: threshold 4
+    // with P biased by 2^4, so the largest P of a row lies in [2^4, 2^8].  The bias multiplies P and
+    // the row sum alike and cancels in O / l.
+    constexpr float kRescale = kFp8 ? 4.0f : (kFp16 ? 12.0f : 24.0f);
+    constexpr float kBias = kFp8 ? 4.0f : 0.0f;
     int g = 0;      // tiles processed by this CTA so far
     int ic = 0;     // items processed by this CTA so far
     bool ok = true;
@@ -254,12 +267,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       uint8_t* out;          // this row's output + column offset, or null for a padding row
       const uint8_t* res;    // residual row + column offset, or null
       float* lse;            // stream A only, or null
+      float vscale;          // e4m3: scale_v[b,h]; else 1
     };
-    Epi epi{nullptr, nullptr, nullptr};
+    Epi epi{nullptr, nullptr, nullptr, 1.f};
     uint4 resv[kHalf / 8];
     auto epilogue_prepare = [&](const Item& it) {
       // pointers of this row; issue the residual reads (they complete during the item's last tile)
-      epi = Epi{nullptr, nullptr, nullptr};
+      epi = Epi{nullptr, nullptr, nullptr, kFp8 ? p.scale_v[it.bh] : 1.f};
 #pragma unroll
       for (int i = 0; i < kHalf / 8; ++i) resv[i] = make_uint4(0, 0, 0, 0);
       if (r_in < it.rows_valid) {
@@ -289,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       const float fa = ex2_approx(sa.x - m_all), fb = ex2_approx(sb.x - m_all);
       const float l_all = sa.y * fa + sb.y * fb;
       const float inv_l = 1.f / l_all;
-      const float wa = fa * inv_l, wb = fb * inv_l;
+      const float wa = fa * inv_l * epi.vscale, wb = fb * inv_l * epi.vscale;
       const uint32_t tOa = tmem + kColO + x * kHalf + lane_addr;
       const uint32_t tOb = tmem + kColO + 128 + x * kHalf + lane_addr;
 #pragma unroll
@@ -322,7 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         }
       }
       // natural-log LSE of the scaled logits
-      if (epi.lse != nullptr) *epi.lse = (m_all + lg2_approx(l_all)) * 0.6931471805599453f;
+      if (epi.lse != nullptr) *epi.lse = (m_all + lg2_approx(l_all) - kBias) * 0.6931471805599453f;
       return true;
     };
 
@@ -330,6 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 #pragma unroll 1
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
       const Item it = decode_item(p, item);
+      if (kFp8) scale_log2 = p.scale_qk_log2[item];
       float m_run = -INFINITY;   // running (possibly stale) row max, log2 domain
       float l_run = 0.f;         // running row sum relative to m_run
 #pragma unroll 1
@@ -385,21 +400,28 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
               }
             }
 #pragma unroll 1
-            for (int c = 0; c < 2 * q; ++c) {
+            for (int c = 0; c < (kFp8 ? q : 2 * q); ++c) {      // 8 columns = 16 (16-bit) or 32 (8-bit) values
               uint32_t r[8];
               tmem_ld8(tSx + c * 8, r);
               tmem_wait_ld();
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float2 f = unpack16<kFp16>(r[i]);
-                r[i] = pack16<kFp16>(f.x * alpha, f.y * alpha);
+                if constexpr (kFp8) {
+                  float f[4];
+                  unpack_e4m3x4(r[i], f);
+                  r[i] = pack_e4m3x4(f[0] * alpha, f[1] * alpha, f[2] * alpha, f[3] * alpha);
+                } else {
+                  const float2 f = unpack16<kFp16>(r[i]);
+                  r[i] = pack16<kFp16>(f.x * alpha, f.y * alpha);
+                }
               }
               tmem_st8(tSx + c * 8, r);
             }
             TR_END(4);   // rescale (rare)
           }
-          const float neg_m = -m_run;
+          const float neg_m = kBias - m_run;
           float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+          uint32_t pk8[8];       // e4m3 only: the chunk's 32 values
 #pragma unroll
           for (int h2 = 0; h2 < 2; ++h2) {
             uint32_t pk[8];
@@ -414,11 +436,16 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
               ls1 += p1;
               ls2 += p2;
               ls3 += p3;
-              pk[i] = pack16<kFp16>(p0, p1);
-              pk[i + 1] = pack16<kFp16>(p2, p3);
+              if constexpr (kFp8) {
+                pk8[h2 * 4 + i / 2] = pack_e4m3x4(p0, p1, p2, p3);
+              } else {
+                pk[i] = pack16<kFp16>(p0, p1);
+                pk[i + 1] = pack16<kFp16>(p2, p3);
+              }
             }
-            tmem_st8(tSx + q * 16 + h2 * 8, pk);
+            if constexpr (!kFp8) tmem_st8(tSx + q * 16 + h2 * 8, pk);
           }
+          if constexpr (kFp8) tmem_st8(tSx + q * 8, pk8);
           l_run += (ls0 + ls1) + (ls2 + ls3);
         }
         if (!ok) break;
@@ -466,8 +493,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     const int pw = warp - kProducerWarp0;
     const int row0 = pw * kRowsPerProducerWarp;
     const int my_row = row0 + lane;                              // tile row / query row of this thread
-    const int chunk_off = (lane % (D / 8)) * 16;                 // this lane's 16-byte chunk inside a row
-    const size_t q_row = 2 * (size_t)p.q_stride[1], k_row = 2 * (size_t)p.k_stride[1], v_row = 2 * (size_t)p.v_stride[1];
+    const int chunk_off = (lane % (RB / 16)) * 16;               // this lane's 16-byte chunk inside a row
+    const size_t q_row = kEs * (size_t)p.q_stride[1], k_row = kEs * (size_t)p.k_stride[1], v_row = kEs * (size_t)p.v_stride[1];
     int slot = 0, slot_phase = 0;   // ring position; the phase flips every wrap
     bool wrapped = false;
     bool ok = true;
@@ -499,8 +526,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (ic >= 2) ok = ok && mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((ic >> 1) - 1) & 1, p.status, 22);
       if (!ok) return;
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
-                          2 * ((size_t)it.b * p.q_stride[0] + (size_t)it.h * p.q_stride[2]) + chunk_off;
-      warp_gather_rows<D>(sQ(qbuf), row0, src_row, qb, q_row, lane);
+                          kEs * ((size_t)it.b * p.q_stride[0] + (size_t)it.h * p.q_stride[2]) + chunk_off;
+      warp_gather_rows<RB>(sQ(qbuf), row0, src_row, qb, q_row, lane);
       cp_async_arrive_noinc(bar(BAR_Q_FULL + qbuf));
     };
 
@@ -510,7 +537,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (!ok) return;
       TR_END(1);   // wait for a free ring slot
       // raw index, clamped only here: the global load issued one step earlier stays in flight until now
-      warp_gather_rows<D>(sRing(slot), row0, min(max(idx, 0), p.Sk - 1), lane_src, row_bytes, lane);
+      warp_gather_rows<RB>(sRing(slot), row0, min(max(idx, 0), p.Sk - 1), lane_src, row_bytes, lane);
       cp_async_arrive_noinc(bar(BAR_FULL + slot));
       TR_END(2);   // issue the tile's cp.async
       if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
@@ -526,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       const Item it = decode_item(p, c.item);
       c.T = it.T;
       c.gi = it.gi + my_row;
-      c.kv = reinterpret_cast<const uint8_t*>(tensor) + 2 * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
+      c.kv = reinterpret_cast<const uint8_t*>(tensor) + kEs * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
     };
     auto load_idx = [&](const Cur& c) { return __ldg(c.gi + c.t * kTileN); };
 
@@ -587,7 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     // and ring positions are tracked incrementally.
     // =====================================================================
     if (lane == 0 && blockIdx.x < n_items) {
-      constexpr uint32_t kFmt = kFp16 ? 0u : 1u;
+      constexpr uint32_t kFmt = (kFp16 || kFp8) ? 0u : 1u;   // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
       constexpr uint32_t idesc_qk = mma_idesc(kFmt, kFmt, 0, 0, 128, kTileN);
       constexpr uint32_t idesc_pv = mma_idesc(kFmt, kFmt, 0, 1, 128, D);
       // descriptor high word: stride byte offset 1024, version 1, 128-byte swizzle
@@ -615,10 +642,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         const uint32_t qlo = ((sQ(qbuf) & 0x3FFFFu) >> 4) | kLboK;
         const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboK;
 #pragma unroll
-        for (int j = 0; j < D / 16; ++j) {
-          constexpr uint32_t kStep = 32 >> 4;   // 16 elements = 32 bytes inside the 128-byte swizzle span
+        for (int j = 0; j < RB / 32; ++j) {
+          // one k-step = 32 bytes of every row (16 16-bit or 32 8-bit elements) inside the 128-byte swizzle span
+          constexpr uint32_t kStep = 32 >> 4;
           const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * kStep;
-          mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+          if constexpr (kFp8) mma_f8_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+          else mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
         }
         TR_END(2);   // issue QK MMAs
         tc_commit(bar(BAR_EMPTY + slot));
@@ -645,9 +674,18 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           const uint32_t tP = tmem + kColS + buf * 128 + x * 64;
           const uint32_t tO = tmem + kColO + x * 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // A: 16 packed 16-bit values = 8 TMEM columns per k-step; B: 16 KV rows = 2048 bytes
-            mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (j > 0));
+          if constexpr (kFp8) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              // A: 32 e4m3 values = 8 TMEM columns per k-step; B: 32 KV rows of 128 bytes = 4096 bytes
+              mma_f8_ts(tO, tP + j * 8, desc(vlo + (x * 2 + j) * (4096 >> 4)), idesc_pv, (t > 0) || (j > 0));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // A: 16 packed 16-bit values = 8 TMEM columns per k-step; B: 16 KV rows = 2048 bytes
+              mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (j > 0));
+            }
           }
           TR_END(8);   // issue PV MMAs
         }
@@ -722,10 +760,10 @@ int num_sms() {
   return cached[dev];
 }
 
-template <int D, bool kFp16>
+template <int D, int kType>
 int launch(const GatherAttnParams& p, cudaStream_t stream) {
-  using L = Smem<D>;
-  auto kern = gather_attn_kernel<D, kFp16>;
+  using L = Smem<D * (kType == 2 ? 1 : 2)>;
+  auto kern = gather_attn_kernel<D, kType>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return -8;
   const long long items = (long long)p.B * p.H * p.M;
@@ -737,8 +775,13 @@ int launch(const GatherAttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream) {
-  if (p.D == 128) return fp16 ? launch<128, true>(p, stream) : launch<128, false>(p, stream);
-  if (p.D == 64) return fp16 ? launch<64, true>(p, stream) : launch<64, false>(p, stream);
+  if (p.D == 128) return fp16 ? launch<128, 1>(p, stream) : launch<128, 0>(p, stream);
+  if (p.D == 64) return fp16 ? launch<64, 1>(p, stream) : launch<64, 0>(p, stream);
+  return -3;
+}
+
+int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream) {
+  if (p.D == 128) return launch<128, 2>(p, stream);
   return -3;
 }
 

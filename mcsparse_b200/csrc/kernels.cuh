@@ -76,5 +76,6 @@ struct TopkParams {
 int launch_topk_select(const TopkParams& p, cudaStream_t stream);
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
+int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
 
 }  // namespace mcs

@@ -7,6 +7,7 @@
 // shows up as a non-zero status instead of a hung GPU.
 #pragma once
 #include <cstdint>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 namespace mcs {
@@ -369,6 +370,34 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+// four floats -> four e4m3 bytes (a in the lowest byte), round to nearest, saturating
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n\t"
+      ".reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t"
+      "}\n"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+// four e4m3 bytes -> four floats
+__device__ __forceinline__ void unpack_e4m3x4(uint32_t u, float (&f)[4]) {
+  uint32_t h0, h1;
+  asm("{\n\t"
+      ".reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t"
+      "}\n"
+      : "=r"(h0), "=r"(h1)
+      : "r"(u));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }

@@ -155,3 +155,199 @@ def _select_topk_tokens(token_probs, topk_ratio, tile_n=128, ds_k=1, orig_L_K=No
     gi = select_topk_with_sinks(scores, count, sink_ranges)
     lengths = torch.full((B, H, M), count // tile_n, dtype=torch.int32, device=token_probs.device)
     return gi, lengths
+
+
+# =============================================================================================
+# Host-side state of token-sparse attention: configuration, per-layer cache, step modes.
+# Mirrors TokenSparseConfig (token_sparse.py:104-198), TokenSparseCache (:200-547, mode :233-247),
+# TokenSparseBackend (:1013-1459) and TokenSparseContext (:1461-1845) for the options that lie on
+# the accelerated path.  What the reference implements with a chain of torch ops and copies is one
+# kernel call here: Q is read through the permutation, the residual is added in the epilogue and
+# the output is written back in the original order.
+# =============================================================================================
+from dataclasses import dataclass, field
+from typing import List, Tuple, Union
+
+
+@dataclass
+class TokenSparseConfig:
+    """Token-level sparse attention settings (same names and defaults as the reference's)."""
+    topk: float = 0.1
+    topp: Optional[float] = None
+    selection_mode: str = 'topk'
+    BLKQ: int = 128
+    tile_n: int = 128
+    sink_ranges: Optional[List[Tuple[int, int]]] = None
+    calibrate_steps: Optional[List[int]] = None
+    update_steps: Optional[List[int]] = None
+    full_steps: Optional[List[int]] = None
+    full_layers: List[int] = field(default_factory=list)
+    share_lse: bool = False
+    cal_downsample: Union[int, Tuple[int, int]] = 1
+    bias_correction: bool = False
+    pca_reorder: bool = False
+    pca_pow_iters: int = 4
+    pca_seed: int = 0
+
+    def __post_init__(self):
+        assert 0 < self.topk <= 1.0
+        assert self.selection_mode in ('topk', 'topp', 'topk_topp'), \
+            f"selection_mode must be 'topk', 'topp', or 'topk_topp', got '{self.selection_mode}'"
+        if self.selection_mode != 'topk':
+            raise NotImplementedError("only selection_mode='topk' runs on the accelerated path")
+        assert self.BLKQ == 128
+        assert self.tile_n == 128
+        if isinstance(self.cal_downsample, (list, tuple)):
+            ds = (int(self.cal_downsample[0]), int(self.cal_downsample[1]))
+        else:
+            ds = (int(self.cal_downsample),) * 2
+        if ds != (1, 1):
+            raise NotImplementedError("cal_downsample > 1 is not part of the accelerated path")
+        self._cal_ds_q, self._cal_ds_k = ds
+        self._calibrate_set = set(self.calibrate_steps) if self.calibrate_steps else None
+        self._update_set = set(self.update_steps) if self.update_steps else None
+        self._full_set = set(self.full_steps) if self.full_steps else None
+        if self.sink_ranges:
+            for start, end in self.sink_ranges:
+                assert 0 <= start < end, f"Invalid sink_ranges interval: ({start}, {end})"
+        if self.pca_reorder:
+            assert not self.share_lse, "pca_reorder is incompatible with share_lse"
+
+
+class TokenSparseCache:
+    """Per-layer state carried between denoising steps: permutation, indices, LSE, residual."""
+
+    def __init__(self, config: TokenSparseConfig):
+        self.config = config
+        self._step_count = 0
+        self._cached_lse = None
+        self._cached_indices = None
+        self._cached_lengths = None
+        self._cached_perm = None
+        self._cached_residual = None
+        self._perm_generation = 0          # advances on every permutation refresh
+        self._residual_perm_gen = None     # generation the residual was computed under
+        self._cached_len = None
+
+    @property
+    def has_cache(self) -> bool:
+        return self._cached_indices is not None
+
+    @property
+    def mode(self) -> str:
+        """Mode of the current step (token_sparse.py:233-247)."""
+        s, c = self._step_count, self.config
+        if c._full_set and s in c._full_set:
+            if c._calibrate_set and s in c._calibrate_set:
+                return 'full_calibrate'
+            return 'full'
+        if c._calibrate_set and s in c._calibrate_set:
+            return 'calibrate'
+        if c._update_set and s in c._update_set:
+            return 'update'
+        if not self.has_cache:
+            return 'calibrate'
+        return 'reuse'
+
+    def step(self) -> None:
+        self._step_count += 1
+
+    def reset(self) -> None:
+        self.__init__(self.config)
+
+    def residual_if_valid(self):
+        """The cached residual, unless it belongs to an older permutation (token_sparse.py:505-521)."""
+        if self._cached_residual is None:
+            return None
+        if self.config.pca_reorder and self._residual_perm_gen != self._perm_generation:
+            self._cached_residual = None
+            return None
+        return self._cached_residual
+
+
+def dense_attention_with_lse(q, k, v, scale):
+    """Dense attention output and natural-log LSE on (B,H,L,D) tensors.
+
+    The input of the anchor step (the reference calls FA3 here, ops/full_attn.py:88-121).  This is a
+    library call (torch's flash attention), not one of this package's kernels.
+    """
+    out, lse = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, False, False, scale=scale)[:2]
+    return out, lse.float()
+
+
+class TokenSparseBackend:
+    """One attention call of one layer, on (B, H, L, D) tensors, by the mode of the layer's cache."""
+
+    def __init__(self, config: TokenSparseConfig):
+        self.config = config
+
+    def _sparse(self, q, k, v, gi, gl, scale, residual, perm):
+        from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import flash_attn_gather_kv_func
+        # (B,H,L,D) storage viewed as (B,L,H,D): no copies, the kernel takes the strides
+        out = torch.empty_like(q)
+        flash_attn_gather_kv_func(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gi, softmax_scale=scale,
+                                  gather_kv_lengths=gl, out=out.transpose(1, 2), residual=residual, perm=perm)
+        return out
+
+    def forward(self, cache: TokenSparseCache, q, k, v, scale: Optional[float] = None):
+        from mcsparse_b200.kernels.flash_mcsa.pca_group import apply_perm_bhld, pca_group_perm
+        cfg = self.config
+        B, H, L, D = q.shape
+        if scale is None:
+            scale = 1.0 / math.sqrt(D)
+        if cache._cached_len is not None and cache._cached_len != (L, k.shape[2]):
+            cache.reset()                                           # length change forces a new anchor step
+        mode = cache.mode
+        if mode == 'full':
+            return dense_attention_with_lse(q, k, v, scale)[0]
+        if mode in ('calibrate', 'full_calibrate'):
+            perm = None
+            if cfg.pca_reorder:
+                perm = pca_group_perm(q.reshape(B * H, L, D), C=cfg.BLKQ, pow_iters=cfg.pca_pow_iters, seed=cfg.pca_seed)
+                cache._perm_generation += 1
+            cache._cached_perm = perm
+            q_grp = q if perm is None else apply_perm_bhld(q, perm)
+            dense_grp, lse = dense_attention_with_lse(q_grp, k, v, scale)        # group (permuted) order
+            cache._cached_lse = lse
+            mass = group_mass(q_grp, k, lse, group_rows=cfg.BLKQ, scale=scale)
+            gi, gl = _select_topk_tokens(mass, cfg.topk, tile_n=cfg.tile_n, sink_ranges=cfg.sink_ranges)
+            cache._cached_indices, cache._cached_lengths, cache._cached_len = gi, gl, (L, k.shape[2])
+            if cfg.bias_correction:
+                sparse_grp = self._sparse(q_grp, k, v, gi, gl, scale, None, None)
+                cache._cached_residual = (dense_grp - sparse_grp).to(q.dtype)    # permuted-query order
+                cache._residual_perm_gen = cache._perm_generation
+            if perm is None:
+                return dense_grp
+            from mcsparse_b200.kernels.flash_mcsa.pca_group import invert_perm_bhld
+            return invert_perm_bhld(dense_grp, perm)
+        if mode == 'update':
+            perm = cache._cached_perm
+            q_grp = q if perm is None else apply_perm_bhld(q, perm)
+            mass = group_mass(q_grp, k, cache._cached_lse, group_rows=cfg.BLKQ, scale=scale)
+            cache._cached_indices, cache._cached_lengths = _select_topk_tokens(
+                mass, cfg.topk, tile_n=cfg.tile_n, sink_ranges=cfg.sink_ranges)
+        # reuse (and the attention of an update step): one fused kernel call
+        residual = cache.residual_if_valid() if cfg.bias_correction else None
+        return self._sparse(q, k, v, cache._cached_indices, cache._cached_lengths, scale, residual, cache._cached_perm)
+
+
+class TokenSparseContext:
+    """All layers of a model: one cache per layer, one step clock (token_sparse.py:1461-1845)."""
+
+    def __init__(self, config: TokenSparseConfig, num_layers: int):
+        self.config = config
+        self.backend = TokenSparseBackend(config)
+        self.caches = [TokenSparseCache(config) for _ in range(num_layers)]
+
+    def forward(self, li: int, q, k, v, scale: Optional[float] = None):
+        if li in self.config.full_layers:
+            return dense_attention_with_lse(q, k, v, scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))[0]
+        return self.backend.forward(self.caches[li], q, k, v, scale)
+
+    def step(self) -> None:
+        for c in self.caches:
+            c.step()
+
+    def reset(self) -> None:
+        for c in self.caches:
+            c.reset()

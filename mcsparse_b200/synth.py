@@ -101,3 +101,12 @@ def random_sorted_indices(B, H, M, gather_len, Sk, seed=0, n_sink=N_SINK, device
     rest = scores.topk(gather_len - n_sink, dim=-1).indices + n_sink
     sinks = torch.arange(n_sink, device=device).expand(B, H, M, n_sink)
     return torch.cat([sinks, rest.sort(dim=-1).values], dim=-1).to(torch.int32).contiguous()
+
+
+def quantize_e4m3_per_head(x: torch.Tensor):
+    """Per-head symmetric e4m3 quantisation of a (B, L, H, D) tensor with scale = amax / 448.
+    Returns (x8 float8_e4m3fn, scale (B, H) fp32) with x ~= x8 * scale."""
+    amax = x.float().abs().amax(dim=(1, 3)).clamp_min(1e-12)          # (B, H)
+    scale = amax / 448.0
+    x8 = (x.float() / scale[:, None, :, None]).to(torch.float8_e4m3fn)
+    return x8, scale.to(torch.float32)

@@ -81,3 +81,33 @@ def error_metrics(out: torch.Tensor, ref: torch.Tensor):
     """(max-abs, mean-rel) as used for the stated tolerances: mean|d| / mean|ref|."""
     d = (out.double() - ref.double()).abs()
     return float(d.max()), float(d.mean() / ref.double().abs().mean().clamp_min(1e-30))
+
+
+def gather_attn_fp8_ref(q8, k8, v8, gi, scale_qk_log2, scale_v, gl=None, residual=None, perm=None,
+                        dtype=torch.float32):
+    """FP8 entry point contract (interface.py:358-373, flash_fwd_sm90_fp8.py:19-23, 145-241):
+    logits in the log2 domain are ``(q8 . k8) * scale_qk_log2[b,h,m]``; the output is
+    ``softmax(...) @ v8 * scale_v[b,h]``.  The kernel's internal P quantisation and 2^k offsets are
+    implementation details covered by the tolerance.  q8/k8/v8: float8_e4m3fn (B,S,H,D)."""
+    B, Sq, H, D = q8.shape
+    M = gi.shape[2]
+    qf, kf, vf = q8.to(dtype), k8.to(dtype), v8.to(dtype)
+    out = torch.zeros(B, Sq, H, D, dtype=dtype)
+    lse = torch.zeros(B, H, Sq, dtype=dtype)
+    ln2 = math.log(2.0)
+    for b in range(B):
+        for h in range(H):
+            p = perm[b * H + h].long() if perm is not None else None
+            for m in range(M):
+                lo, hi = m * 128, min((m + 1) * 128, Sq)
+                n = gi.shape[-1] if gl is None else int(gl[b, h, m]) * 128
+                idx = gi[b, h, m, :n].long()
+                rows = torch.arange(lo, hi)
+                src = p[rows] if p is not None else rows
+                s = (qf[b, src, h] @ kf[b, idx, h].T) * float(scale_qk_log2[b, h, m]) * ln2
+                o = torch.softmax(s, dim=-1) @ vf[b, idx, h] * float(scale_v[b, h])
+                if residual is not None:
+                    o = o + residual[b, h, lo:hi].to(dtype)
+                out[b, src, h] = o
+                lse[b, h, src] = torch.logsumexp(s, dim=-1)
+    return out, lse
