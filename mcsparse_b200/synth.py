@@ -110,3 +110,22 @@ def quantize_e4m3_per_head(x: torch.Tensor):
     scale = amax / 448.0
     x8 = (x.float() / scale[:, None, :, None]).to(torch.float8_e4m3fn)
     return x8, scale.to(torch.float32)
+
+
+def topmass_indices(q: torch.Tensor, k: torch.Tensor, shape: VideoShape, heads_per_chunk: int = 4) -> torch.Tensor:
+    """Anchor-step selection with this package's own kernels, as the benchmark configuration defines its
+    indices: per query group the 4 sink tokens plus the (topk - 4) tokens of highest exact fp32 group
+    mass, ascending int32 (1, H, M, topk).  q, k: (1, L, H, D) CUDA tensors.  The dense log-sum-exp that
+    the mass needs comes from torch's flash attention (an input of the anchor step, not part of it)."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import dense_attention_with_lse, group_mass, select_topk_with_sinks
+    H, D = q.shape[2], q.shape[3]
+    scale = 1.0 / math.sqrt(D)
+    out = torch.empty(1, H, shape.n_groups, shape.topk, dtype=torch.int32, device=q.device)
+    for h0 in range(0, H, heads_per_chunk):
+        h1 = min(H, h0 + heads_per_chunk)
+        qh = q[:, :, h0:h1].transpose(1, 2)            # (1, h, L, D) views
+        kh = k[:, :, h0:h1].transpose(1, 2)
+        _, lse = dense_attention_with_lse(qh.contiguous(), kh.contiguous(), kh.contiguous(), scale)
+        mass = group_mass(qh, kh, lse, group_rows=shape.group_rows, scale=scale)
+        out[:, h0:h1] = select_topk_with_sinks(mass, shape.topk, [(0, N_SINK)])
+    return out

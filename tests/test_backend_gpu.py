@@ -1,0 +1,69 @@
+"""GPU end-to-end: anchor step then reuse steps through the host-side state machine, against the oracle's
+composition of the same stages (dense attention, exact mass, selection, sparse attention + residual)."""
+
+import math
+
+import pytest
+import torch
+
+from oracle.gather_attn import dense_attn_ref, error_metrics, gather_attn_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _qkv(B, H, L, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    cent = torch.randn(H, 16, D, generator=g)
+    cid = torch.randint(0, 16, (L,), generator=g)
+    mk = lambda: (cent[:, cid].unsqueeze(0) + 0.3 * torch.randn(B, H, L, D, generator=g)).to(torch.bfloat16)
+    return mk(), mk(), torch.randn(B, H, L, D, generator=g).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("pca", [False, True])
+def test_calibrate_then_reuse(cuda_device, pca):
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    B, H, L, D = 1, 2, 1500, 128
+    cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], sink_ranges=[(0, 4)], bias_correction=True, pca_reorder=pca,
+                            pca_pow_iters=4)
+    ctx = TokenSparseContext(cfg, num_layers=1)
+    q, k, v = _qkv(B, H, L, D, 1)
+    dev = cuda_device
+    # step 0: anchor step returns the dense result
+    out0 = ctx.forward(0, q.to(dev), k.to(dev), v.to(dev)).float().cpu()
+    dense, _ = dense_attn_ref(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+    mx, mr = error_metrics(out0.transpose(1, 2), dense)
+    assert mx < 2e-2 and mr < 1e-2, (mx, mr)
+    cache = ctx.caches[0]
+    gi, gl, perm, res = cache._cached_indices, cache._cached_lengths, cache._cached_perm, cache._cached_residual
+    assert gi.shape[-1] % 128 == 0 and (gi[..., :4].cpu() == torch.arange(4)).all() and res is not None
+    assert (perm is not None) == pca
+    # reuse step on the SAME q/k/v: sparse + cached residual must reproduce the dense output
+    ctx.step()
+    assert cache.mode == "reuse"
+    out1 = ctx.forward(0, q.to(dev), k.to(dev), v.to(dev)).float().cpu()
+    mx, mr = error_metrics(out1.transpose(1, 2), dense)
+    assert mx < 3e-2 and mr < 1.5e-2, (mx, mr)
+    # reuse step on fresh q/k/v: equals the oracle's sparse attention with the cached metadata
+    ctx.step()
+    q2, k2, v2 = _qkv(B, H, L, D, 2)
+    out2 = ctx.forward(0, q2.to(dev), k2.to(dev), v2.to(dev)).float().cpu()
+    ref2, _ = gather_attn_ref(q2.transpose(1, 2), k2.transpose(1, 2), v2.transpose(1, 2), gi.cpu(),
+                              gl=None if gl is None else gl.cpu(), residual=res.cpu(),
+                              perm=None if perm is None else perm.cpu())
+    mx, mr = error_metrics(out2.transpose(1, 2), ref2)
+    assert mx < 2e-2 and mr < 1e-2, (mx, mr)
+
+
+def test_topmass_indices_helper(cuda_device):
+    from mcsparse_b200 import synth
+    from oracle.group_mass import dense_lse_ref, group_mass_ref
+    from oracle.select import select_topk_ref
+    shape = synth.VideoShape("tiny", 2, (4, 10, 16), (2, 5, 4), topk=256, n_centroids=8)
+    q, k, _ = synth.clustered_qkv(shape, device=cuda_device)
+    gi = synth.topmass_indices(q, k, shape).cpu()
+    qh, kh = q.cpu().transpose(1, 2), k.cpu().transpose(1, 2)
+    mass = group_mass_ref(qh, kh, dense_lse_ref(qh, kh).float())
+    ref = select_topk_ref(mass.float(), 256, range(4))
+    # selection from the kernel's own fp32 mass is exact; against the fp64 oracle mass near-ties may swap
+    agree = (gi == ref).float().mean().item()
+    assert agree > 0.97, agree
