@@ -170,6 +170,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     shape = synth.C2
+    if args.heads:
+        # reduced head count: a small case of the same kernel for profiler captures, not a bench line
+        import dataclasses
+        shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
     H, L, D = shape.heads, shape.seq_len, shape.head_dim
     if H % world or L % world:
         raise RuntimeError(f"heads ({H}) and sequence ({L}) must divide by the number of ranks ({world})")
@@ -298,6 +302,69 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_anchor(args):
+    """Secondary measurement: the anchor-step (metadata build) kernels at the same shape, each timed alone
+    with CUDA events on resident inputs: group mass, top-k selection, Fast PDDP, permutation apply/invert."""
+    import math
+    import torch
+    from mcsparse_b200 import _lib, synth
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import apply_perm, invert_perm, pca_group_perm, pddp_start_vectors
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import dense_attention_with_lse, group_mass, select_topk_with_sinks
+    os.environ["MCSPARSE_B200_CHECK"] = "0"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = synth.C2
+    H = args.heads or shape.heads
+    L, D = shape.seq_len, shape.head_dim
+    q, k, _ = synth.clustered_qkv(shape, heads=H, device=dev)
+    qh, kh = q.transpose(1, 2), k.transpose(1, 2)
+    scale = 1.0 / math.sqrt(D)
+    lse = torch.cat([dense_attention_with_lse(qh[:, h:h + 1].contiguous(), kh[:, h:h + 1].contiguous(),
+                                              kh[:, h:h + 1].contiguous(), scale)[1] for h in range(H)], 1)
+
+    def timeit(fn):
+        for _ in range(max(1, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in ev)
+
+    peaks = _peaks()
+    mass = torch.empty(1, H, shape.n_groups, L, dtype=torch.float32, device=dev)
+    gi = torch.empty(1, H, shape.n_groups, shape.topk, dtype=torch.int32, device=dev)
+    x = q[0].transpose(0, 1)
+    sv = pddp_start_vectors(H, L, 128, D, 0).to(dev)
+    t_mass = timeit(lambda: group_mass(qh, kh, lse, out=mass))
+    t_topk = timeit(lambda: select_topk_with_sinks(mass, shape.topk, [(0, 4)], out=gi))
+    t_pddp = timeit(lambda: pca_group_perm(x, C=128, pow_iters=8, start_vectors=sv))
+    perm = pca_group_perm(x, C=128, pow_iters=8, start_vectors=sv)
+    xc = x.contiguous()
+    t_app = timeit(lambda: apply_perm(xc, perm))
+    t_inv = timeit(lambda: invert_perm(xc, perm))
+    _lib.check_status(dev, "anchor bench")
+    levels = 8
+    rows = {
+        "group_mass": {"ms": t_mass, "tflops": 2.0 * L * L * D * H / t_mass / 1e9, "gexp_per_s": L * L * H / t_mass / 1e6,
+                       "bound": "sfu ex2 (16/clk/SM) and tensor"},
+        "topk_select": {"ms": t_topk, "gbs": (mass.numel() * 4 + gi.numel() * 4) / t_topk / 1e6, "bound": "hbm",
+                        "frac": (mass.numel() * 4 + gi.numel() * 4) / t_topk / 1e6 / peaks["hbm_gbs"]},
+        "pddp_perm": {"ms": t_pddp, "gbs": levels * 2 * x.numel() * 2 / t_pddp / 1e6, "bound": "hbm",
+                      "frac": levels * 2 * x.numel() * 2 / t_pddp / 1e6 / peaks["hbm_gbs"]},
+        "perm_apply": {"ms": t_app, "gbs": 2 * xc.numel() * 2 / t_app / 1e6, "frac": 2 * xc.numel() * 2 / t_app / 1e6 / peaks["hbm_gbs"]},
+        "perm_invert": {"ms": t_inv, "gbs": 2 * xc.numel() * 2 / t_inv / 1e6, "frac": 2 * xc.numel() * 2 / t_inv / 1e6 / peaks["hbm_gbs"]},
+    }
+    total = t_mass + t_topk + t_pddp
+    print(json.dumps({"metric": "anchor_metadata_build_ms", "value": total, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(1, args.warmup), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"anchor_L{L}_H{H}_D{D}_topk{shape.topk}_pddp8"}, "kernels": rows,
+                      "peak_source": peaks["source"]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -306,9 +373,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
+    ap.add_argument("--workload", default="attn", choices=["attn", "anchor"],
+                    help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "anchor":
+        run_anchor(args)
     else:
         run_ours(args)
 
