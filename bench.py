@@ -188,18 +188,22 @@ def run_ours(args):
     out = torch.empty_like(q)
 
     if world > 1:
-        from mcsparse_b200.h3.context_parallel import UlyssesReshard
-        resh = UlyssesReshard(dist.group.WORLD, L, H, D, torch.bfloat16, dev)
+        from mcsparse_b200.h3.context_parallel import UlyssesSparseAttention
+        ul = UlyssesSparseAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
         Ls = L // world
         q_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
         k_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
         v_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
+        o_chunks = [torch.empty(1, L, ul.hc, D, device=dev, dtype=torch.bfloat16) for _ in range(ul.chunks)]
+
+        def attn(qh, kh, vh, h0, h1):
+            o = o_chunks[h0 // ul.hc]
+            flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], out=o, residual=residual[:, h0:h1])
+            return o
 
         def step():
-            qh, kh, vh = resh.seq_to_head(q_s, k_s, v_s)
-            o, _ = flash_attn_gather_kv_func(qh, kh, vh, gi, residual=residual)
-            return resh.head_to_seq(o)
-        launches_per_step = 1 + resh.kernels_per_step
+            return ul.forward(q_s, k_s, v_s, attn)
+        launches_per_step = ul.chunks
     else:
         def step():
             flash_attn_gather_kv_func(q, k, v, gi, out=out, residual=residual)
@@ -373,6 +377,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chunks", type=int, default=3, help="head chunks of the Ulysses pipeline (N > 1)")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU)")

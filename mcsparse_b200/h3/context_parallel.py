@@ -98,3 +98,107 @@ class UlyssesReshard:
         self._a2a([send], [self._orecv])
         # received block i holds heads [i*Hl, (i+1)*Hl) of this rank's tokens
         return self._orecv.permute(1, 2, 0, 3, 4).reshape(B, Ls, self.H, D)
+
+
+class UlyssesSparseAttention:
+    """Ulysses attention core with the two all-to-alls overlapped with the attention kernel.
+
+    The local heads are processed in chunks: while the attention kernel works on chunk c (compute stream),
+    the all-to-all of chunk c+1 runs on a communication stream, and the reverse all-to-all of finished chunks
+    runs on a second communication stream with its own communicator (two NCCL operations of one communicator
+    must not run concurrently).  Received data always lands in this rank's own buffers; the attention kernel
+    reads them in place through strides (no unpack copy on the way in, no pack copy on the way out for B == 1).
+
+    ``attn_fn(q, k, v, h0, h1)`` gets (1, L, hc, D) tensors of local heads [h0, h1) and returns (1, L, hc, D).
+    Replaces the role of diffusers' ``_templated_context_parallel_attention`` in the reference
+    (mcsparse/h3/context_parallel.py:220-229) for batch size 1.
+    """
+
+    def __init__(self, group, seq_len: int, heads: int, head_dim: int, dtype, device, chunks: int = 3):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if heads % self.world or seq_len % self.world:
+            raise ValueError(f"Ulysses needs heads ({heads}) and sequence ({seq_len}) divisible by the ranks ({self.world})")
+        self.L, self.H, self.D = seq_len, heads, head_dim
+        self.Ls, self.Hl = seq_len // self.world, heads // self.world
+        self.chunks = max(1, min(chunks, self.Hl))
+        while self.Hl % self.chunks:
+            self.chunks -= 1
+        self.hc = self.Hl // self.chunks
+        N, Ls, hc, D = self.world, self.Ls, self.hc, head_dim
+        mk = lambda: torch.empty(N, Ls, hc, D, dtype=dtype, device=device)
+        self._send = [[mk() for _ in range(3)] for _ in range(self.chunks)]
+        self._recv = [[mk() for _ in range(3)] for _ in range(self.chunks)]
+        self._orecv = [mk() for _ in range(self.chunks)]
+        self._out = torch.empty(1, Ls, heads, head_dim, dtype=dtype, device=device)
+        self.is_cuda = torch.device(device).type == "cuda"
+        # second communicator for the reverse direction (every rank must create it)
+        self.group_back = dist.new_group(ranks=list(range(self.world))) if self.world > 1 else None
+        if self.is_cuda:
+            self.s_fwd, self.s_bwd = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.kernels_per_step = 0
+
+    def _a2a(self, sends, recvs, group):
+        if self.world == 1:
+            for s, r in zip(sends, recvs):
+                r.copy_(s)
+            return
+        if dist.get_backend(group) == "nccl":
+            ops = []
+            for s, r in zip(sends, recvs):
+                for peer in range(self.world):
+                    g = dist.get_global_rank(group, peer)
+                    ops.append(dist.P2POp(dist.isend, s[peer], g, group))
+                    ops.append(dist.P2POp(dist.irecv, r[peer], g, group))
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        else:
+            for s, r in zip(sends, recvs):
+                dist.all_to_all_single(r.view(-1), s.view(-1), group=group)
+
+    def forward(self, q, k, v, attn_fn):
+        """q, k, v: (1, L/N, H, D) sequence shards.  Returns the (1, L/N, H, D) shard of the attention output."""
+        N, Ls, Hl, hc, D = self.world, self.Ls, self.Hl, self.hc, self.D
+        for t in (q, k, v):
+            if tuple(t.shape) != (1, Ls, self.H, D):
+                raise ValueError(f"expected a sequence shard of shape {(1, Ls, self.H, D)}, got {tuple(t.shape)}")
+        views = [t.view(Ls, N, Hl, D) for t in (q, k, v)]
+        out_view = self._out.view(Ls, N, Hl, D)
+        if not self.is_cuda:
+            for c in range(self.chunks):
+                for t, s in zip(views, self._send[c]):
+                    s.copy_(t[:, :, c * hc:(c + 1) * hc].permute(1, 0, 2, 3))
+                self._a2a(self._send[c], self._recv[c], self.group)
+                o = attn_fn(*[r.view(1, N * Ls, hc, D) for r in self._recv[c]], c * hc, (c + 1) * hc)
+                self._a2a([o.contiguous().view(N, Ls, hc, D)], [self._orecv[c]], self.group_back or self.group)
+                out_view[:, :, c * hc:(c + 1) * hc].copy_(self._orecv[c].permute(1, 0, 2, 3))
+            return self._out
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        ev_in = [torch.cuda.Event() for _ in range(self.chunks)]
+        ev_attn = [torch.cuda.Event() for _ in range(self.chunks)]
+        with torch.cuda.stream(self.s_fwd):
+            self.s_fwd.wait_event(ready)
+            for c in range(self.chunks):
+                for t, s in zip(views, self._send[c]):
+                    s.copy_(t[:, :, c * hc:(c + 1) * hc].permute(1, 0, 2, 3))
+                self._a2a(self._send[c], self._recv[c], self.group)
+                ev_in[c].record(self.s_fwd)
+        outs = []
+        for c in range(self.chunks):
+            main.wait_event(ev_in[c])
+            o = attn_fn(*[r.view(1, N * Ls, hc, D) for r in self._recv[c]], c * hc, (c + 1) * hc)
+            outs.append(o)
+            ev_attn[c].record(main)
+            with torch.cuda.stream(self.s_bwd):
+                self.s_bwd.wait_event(ev_attn[c])
+                self._a2a([o.view(N, Ls, hc, D)], [self._orecv[c]], self.group_back)
+                out_view[:, :, c * hc:(c + 1) * hc].copy_(self._orecv[c].permute(1, 0, 2, 3))
+        done = torch.cuda.Event()
+        done.record(self.s_bwd)
+        main.wait_event(done)
+        for o in outs:
+            o.record_stream(self.s_bwd)
+        return self._out

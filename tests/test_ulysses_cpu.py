@@ -34,6 +34,18 @@ def _worker(rank, world, port, B, L, H, D, q):
         back = r.head_to_seq(o)
         expect = full[0].flip(1)[:, rank * Ls:(rank + 1) * Ls]
         ok = ok and torch.equal(back, expect)
+        if B == 1:
+            # chunked attention core: per-head "attention" = reverse the sequence and add the head index
+            from mcsparse_b200.h3.context_parallel import UlyssesSparseAttention
+            ul = UlyssesSparseAttention(dist.group.WORLD, L, H, D, torch.float32, "cpu", chunks=2)
+
+            def attn(qh, kh, vh, h0, h1):
+                hidx = torch.arange(rank * Hl + h0, rank * Hl + h1, dtype=torch.float32).view(1, 1, -1, 1)
+                return qh.flip(1) + kh + 2 * vh + hidx
+            got = ul.forward(*shard, attn)
+            hall = torch.arange(H, dtype=torch.float32).view(1, 1, H, 1)
+            want = (full[0].flip(1) + full[1] + 2 * full[2] + hall)[:, rank * Ls:(rank + 1) * Ls]
+            ok = ok and torch.equal(got, want)
         try:
             UlyssesReshard(dist.group.WORLD, L, H + 1, D, torch.float32, "cpu")
             ok = False
