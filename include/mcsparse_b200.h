@@ -181,6 +181,23 @@ int32_t mcs_pddp_levels(int32_t N, int32_t C);
 int mcs_pddp_perm(const mcs_pddp_args* args, void* stream);
 
 /*
+ * Fast PDDP grouping without a caller-provided workspace.  No counterpart in the reference: this
+ * entry point exists for callers that are not allowed to allocate device memory (a server whose
+ * memory pool owns the whole GPU, a latency path where cudaMalloc is forbidden because it
+ * synchronises the device).  Same arguments and results as mcs_pddp_perm, except that
+ * `workspace` / `workspace_bytes` are ignored: the scratch is a fixed array inside the library's
+ * device image, mcs_pddp_static_scratch_bytes() (32 MiB) large, held by every GPU that loads the
+ * library until the process exits.  Shapes whose mcs_pddp_workspace_bytes() exceeds that size are
+ * rejected with MCS_ERR_TOO_LARGE.  It calls no allocation routine of any kind.
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array and
+ * find the previous call's contents in it (nothing in it needs to start at zero: every region is
+ * written before it is read); two calls that overlap on the GPU, e.g. on different streams, race.
+ */
+int64_t mcs_pddp_static_scratch_bytes(void);
+int mcs_pddp_perm_static(const mcs_pddp_args* args, void* stream);
+
+/*
  * Row permutation of a (BH, L, D) tensor, 16-byte aligned rows of row_bytes bytes, byte strides.
  * apply : out[b, i] = x[b, perm[b, i]]   replaces mcsparse/kernels/flash_mcsa/pca_group.py:40-42, 52-55
  * invert: out[b, perm[b, i]] = x[b, i]   replaces pca_group.py:45-49, 58-61 (no argsort needed)

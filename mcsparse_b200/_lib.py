@@ -30,6 +30,8 @@ EXPORTED_SYMBOLS = (
     "mcs_pddp_start_vector_rows",
     "mcs_pddp_levels",
     "mcs_pddp_perm",
+    "mcs_pddp_static_scratch_bytes",
+    "mcs_pddp_perm_static",
     "mcs_perm_apply",
     "mcs_perm_invert",
 )
@@ -109,6 +111,10 @@ def lib() -> C.CDLL:
     L.mcs_pddp_levels.argtypes = [C.c_int32] * 2
     L.mcs_pddp_perm.restype = C.c_int
     L.mcs_pddp_perm.argtypes = [C.POINTER(PddpArgs), C.c_void_p]
+    L.mcs_pddp_static_scratch_bytes.restype = C.c_int64
+    L.mcs_pddp_static_scratch_bytes.argtypes = []
+    L.mcs_pddp_perm_static.restype = C.c_int
+    L.mcs_pddp_perm_static.argtypes = [C.POINTER(PddpArgs), C.c_void_p]
     for fn in (L.mcs_perm_apply, L.mcs_perm_invert):
         fn.restype = C.c_int
         fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,

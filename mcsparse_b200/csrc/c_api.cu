@@ -147,6 +147,21 @@ int mcs_pddp_perm(const mcs_pddp_args* a, void* stream) {
   return mcs::launch_pddp(p, static_cast<cudaStream_t>(stream));
 }
 
+int64_t mcs_pddp_static_scratch_bytes(void) { return (int64_t)mcs::pddp_static_scratch_bytes(); }
+
+int mcs_pddp_perm_static(const mcs_pddp_args* a, void* stream) {
+  if (a == nullptr) return MCS_ERR_NULL_POINTER;
+  if (a->BH < 1 || a->N < 1 || a->C < 1) return MCS_ERR_BAD_SHAPE;
+  const size_t need = mcs::pddp_workspace_bytes(a->BH, a->N, a->C);
+  if (need == 0 || need > mcs::pddp_static_scratch_bytes()) return MCS_ERR_TOO_LARGE;   // beyond the built-in scratch
+  void* scratch = mcs::pddp_static_scratch_address();     // first call on a device resolves the symbol
+  if (scratch == nullptr) return MCS_ERR_LAUNCH_FAILED;
+  mcs_pddp_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = (int64_t)mcs::pddp_static_scratch_bytes();
+  return mcs_pddp_perm(&b, stream);
+}
+
 static int perm_rows(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes, int64_t x_bh,
                      int64_t x_row, int64_t o_bh, int64_t o_row, bool invert, void* stream) {
   if (x == nullptr || out == nullptr || perm == nullptr) return MCS_ERR_NULL_POINTER;

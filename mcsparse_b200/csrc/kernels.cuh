@@ -61,6 +61,8 @@ size_t pddp_workspace_bytes(int BH, int N, int C);
 long long pddp_start_vector_rows(int BH, int N, int C);
 int pddp_levels(int N, int C);
 int launch_pddp(const PddpArgs& a, cudaStream_t stream);
+size_t pddp_static_scratch_bytes();
+void* pddp_static_scratch_address();
 
 int launch_perm_rows(const void* x, void* out, const long long* perm, int BH, int L, int row_bytes, long long x_bh,
                      long long x_row, long long o_bh, long long o_row, bool invert, cudaStream_t stream);

@@ -532,4 +532,35 @@ int launch_pddp(const PddpArgs& a, cudaStream_t stream) {
 
 int pddp_levels(int N, int C) { return make_plan(1, N, C).levels; }
 
+// ------------------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to hand over a workspace: an inference server that has
+// given every free byte of the GPU to its own memory pool and forbids further allocations, or
+// code on a latency-critical path where cudaMalloc is banned because it synchronises the whole
+// device.  For them the library carries one fixed scratch array in its own device image.  It is
+// part of the module, so each GPU that loads the library pays for it from load to exit: hence
+// the small, fixed size.  In host code the array's name is only a handle, never an address a
+// kernel could use; the usable device address comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+// ------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 32u << 20;   // 32 MiB
+static __device__ __align__(256) unsigned char g_pddp_static_scratch[kStaticScratchBytes];
+
+size_t pddp_static_scratch_bytes() { return kStaticScratchBytes; }
+
+// Device address of the built-in scratch on the CURRENT device (looked up on the first call per
+// device, then cached).  Returns nullptr if the lookup fails.
+void* pddp_static_scratch_address() {
+  static void* cached[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_pddp_static_scratch) != cudaSuccess) return nullptr;
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
 }  // namespace mcs
