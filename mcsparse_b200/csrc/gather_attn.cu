@@ -76,11 +76,13 @@ enum {
   BAR_O_FULL = BAR_PV_DONE + 2,
   BAR_O_EMPTY,
   BAR_STATS,                           // both streams published their (max, sum) of the finished item
-  BAR_DRAIN,
+  BAR_STAGE_FREE,                      // [2] epilogue staging (= Q buffer of the finished item) released
+  BAR_DRAIN = BAR_STAGE_FREE + 2,
   BAR_COUNT
 };
 
-template <int RB>     // RB = bytes per Q/K/V row (head_dim * element size)
+// RB = bytes per Q/K/V row (head_dim * element size); STAGE = bytes of dedicated epilogue staging
+template <int RB, int STAGE>
 struct Smem {
   static constexpr int kBlocks = RB / 128;               // 128-byte column blocks
   static constexpr int kTileBytes = kBlocks * 16384;     // 128 rows x RB bytes
@@ -89,7 +91,11 @@ struct Smem {
   static constexpr int kBars = kRingOff + kRing * kTileBytes;
   static constexpr int kStats = kBars + BAR_COUNT * 8;   // float2 [2 streams][128]
   static constexpr int kTmemSlot = kStats + 2 * 128 * 8;
-  static constexpr int kTotal = kTmemSlot + 16;
+  // Epilogue staging: 256 rows x (head_dim) bytes of 16-bit output halves.  With 16-bit inputs it is
+  // exactly one Q buffer, and the finished item's own Q buffer (idle by then) is used; with 8-bit
+  // inputs the Q buffer is half that size and a dedicated area is carved out instead.
+  static constexpr int kStage = (kTmemSlot + 16 + 127) & ~127;
+  static constexpr int kTotal = kStage + STAGE;
   static constexpr int kDynamic = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
 };
 
@@ -185,7 +191,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
   constexpr bool kFp8 = kType == 2;
   constexpr int kEs = kFp8 ? 1 : 2;              // bytes per Q/K/V element
   constexpr int RB = D * kEs;
-  using L = Smem<RB>;
+  constexpr int kStageDedicated = kFp8 ? 256 * D : 0;   // 16-bit inputs stage in the finished item's Q buffer
+  using L = Smem<RB, kStageDedicated>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
@@ -217,6 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       mbar_init(bar(BAR_P_READY + i), kStreamThreads);
       mbar_init(bar(BAR_P_READY + 2 + i), kStreamThreads);
       mbar_init(bar(BAR_PV_DONE + i), 1);
+      mbar_init(bar(BAR_STAGE_FREE + i), 2 * kStreamThreads);
     }
     mbar_init(bar(BAR_O_FULL), 1);
     mbar_init(bar(BAR_O_EMPTY), 2 * kStreamThreads);
@@ -270,12 +278,21 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       float vscale;          // e4m3: scale_v[b,h]; else 1
     };
     Epi epi{nullptr, nullptr, nullptr, 1.f};
-    uint4 resv[kHalf / 8];
-    auto epilogue_prepare = [&](const Item& it) {
-      // pointers of this row; issue the residual reads (they complete during the item's last tile)
+    // Global traffic of the epilogue is staged through shared memory so that every global access is
+    // coalesced (8 or 4 lanes per 128/64-byte half row): a thread owns a ROW in tensor memory, and 32
+    // row-strided 16-byte accesses per instruction cost the load/store unit 32 wavefronts each.
+    // Each warp has a private 32-row area, XOR-swizzled by row so that both access patterns are
+    // conflict-free.  The residual is brought in with cp.async right after the item's last tile.
+    constexpr int kHalfBytes = kHalf * 2;                 // bytes of this stream's half of an output row
+    constexpr int kCh = kHalfBytes / 16;                  // 16-byte chunks per half row
+    constexpr int kRpi = 32 / kCh;                        // rows covered by one coalesced warp access
+    auto stage_of = [&](int eic) -> uint32_t {
+      const uint32_t base = kFp8 ? (s_base + L::kStage) : sQ(eic & 1);
+      return base + static_cast<uint32_t>(warp) * 32u * kHalfBytes;
+    };
+    bool epi_has_res = false;
+    auto epilogue_prepare = [&](const Item& it, int eic) {
       epi = Epi{nullptr, nullptr, nullptr, kFp8 ? p.scale_v[it.bh] : 1.f};
-#pragma unroll
-      for (int i = 0; i < kHalf / 8; ++i) resv[i] = make_uint4(0, 0, 0, 0);
       if (r_in < it.rows_valid) {
         const int row = it.row_base + r_in;                       // position in (permuted) query order
         long long orow = row;
@@ -284,12 +301,24 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
                   2 * ((size_t)it.b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)it.h * p.o_stride[2] +
                        (size_t)x * kHalf);
         if (x == 0 && p.lse != nullptr) epi.lse = p.lse + (size_t)it.bh * p.Sq + orow;
-        if (p.residual != nullptr) {
-          epi.res = reinterpret_cast<const uint8_t*>(p.residual) +
-                    2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1] + (size_t)row * p.r_stride[2] +
-                         (size_t)x * kHalf);
+      }
+      epi_has_res = p.residual != nullptr;
+      if (epi_has_res) {
+        // residual rows of this warp, coalesced, straight into the staging area
+        const uint8_t* rb = reinterpret_cast<const uint8_t*>(p.residual) +
+                            2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1] + (size_t)x * kHalf);
+        const size_t r_row = 2 * (size_t)p.r_stride[2];
+        const uint32_t st = stage_of(eic);
+        const int w_row0 = (warp & 3) * 32;
+        const int ch = lane % kCh;
 #pragma unroll
-          for (int i = 0; i < kHalf / 8; ++i) resv[i] = ld_nc_v4(epi.res + i * 16);
+        for (int i = 0; i < kCh; ++i) {
+          const int rl = i * kRpi + lane / kCh;                    // row inside the warp's 32 rows
+          const uint32_t dst = st + rl * kHalfBytes + ((ch ^ (rl % kCh)) << 4);
+          if (w_row0 + rl < it.rows_valid)
+            cp_async16(dst, rb + (size_t)(it.row_base + w_row0 + rl) * r_row + ch * 16);
+          else
+            cp_async16_zfill(dst, rb, 0);
         }
       }
     };
@@ -306,6 +335,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       const float wa = fa * inv_l * epi.vscale, wb = fb * inv_l * epi.vscale;
       const uint32_t tOa = tmem + kColO + x * kHalf + lane_addr;
       const uint32_t tOb = tmem + kColO + 128 + x * kHalf + lane_addr;
+      const uint32_t st = stage_of(eic);
+      const uint32_t my_row = st + lane * kHalfBytes;
+      cp_async_wait_all();
+      __syncwarp();
 #pragma unroll
       for (int c = 0; c < kHalf / 16; ++c) {
         uint32_t ra[16], rb[16];
@@ -315,28 +348,41 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         if (c == kHalf / 16 - 1) {
           // all of this thread's reads of O and of the statistics are done
           tc_fence_before();
-          mbar_arrive_relaxed(bar(BAR_O_EMPTY));   // relaxed: must not wait for the output stores in flight
+          mbar_arrive_relaxed(bar(BAR_O_EMPTY));
         }
-        if (epi.out != nullptr) {
 #pragma unroll
-          for (int q4 = 0; q4 < 2; ++q4) {
-            const uint4 res = resv[c * 2 + q4];
-            const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
-            uint32_t ow[4];
+        for (int q4 = 0; q4 < 2; ++q4) {
+          const uint32_t addr = my_row + ((((c * 2 + q4) ^ (lane % kCh))) << 4);
+          uint4 res = make_uint4(0, 0, 0, 0);
+          if (epi_has_res) res = lds_v4(addr);
+          const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
+          uint32_t ow[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 rr = unpack16<kFp16>(rw[j]);
-              const int k = q4 * 8 + 2 * j;
-              const float o0 = fmaf(__uint_as_float(ra[k]), wa, fmaf(__uint_as_float(rb[k]), wb, rr.x));
-              const float o1 = fmaf(__uint_as_float(ra[k + 1]), wa, fmaf(__uint_as_float(rb[k + 1]), wb, rr.y));
-              ow[j] = pack16<kFp16>(o0, o1);
-            }
-            *reinterpret_cast<uint4*>(epi.out + c * 32 + q4 * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          for (int j = 0; j < 4; ++j) {
+            const float2 rr = unpack16<kFp16>(rw[j]);
+            const int k = q4 * 8 + 2 * j;
+            const float o0 = fmaf(__uint_as_float(ra[k]), wa, fmaf(__uint_as_float(rb[k]), wb, rr.x));
+            const float o1 = fmaf(__uint_as_float(ra[k + 1]), wa, fmaf(__uint_as_float(rb[k + 1]), wb, rr.y));
+            ow[j] = pack16<kFp16>(o0, o1);
           }
+          sts_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
       }
       // natural-log LSE of the scaled logits
       if (epi.lse != nullptr) *epi.lse = (m_all + lg2_approx(l_all) - kBias) * 0.6931471805599453f;
+      __syncwarp();
+      // coalesced write-out: kCh lanes per output row
+      const unsigned long long my_out = reinterpret_cast<unsigned long long>(epi.out);
+      const int ch = lane % kCh;
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) {
+        const int rl = i * kRpi + lane / kCh;
+        const unsigned long long optr = __shfl_sync(0xffffffffu, my_out, rl);
+        const uint4 v = lds_v4(st + rl * kHalfBytes + ((ch ^ (rl % kCh)) << 4));
+        if (optr != 0ull) *reinterpret_cast<uint4*>(optr + ch * 16) = v;
+      }
+      __syncwarp();
+      mbar_arrive(bar(BAR_STAGE_FREE + (eic & 1)));          // the staging area (a Q buffer) may be refilled
       return true;
     };
 
@@ -468,9 +514,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           // long true, the wait only matters for items of one or two tiles)
           if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
           if (!ok) break;
+          TR_END(9);   // wait previous O_EMPTY
           stats[x * 128 + r_in] = make_float2(m_run, l_run);
           mbar_arrive(bar(BAR_STATS));
-          epilogue_prepare(it);
+          TR_END(10);  // stats store + arrive
+          epilogue_prepare(it, ic);
           epi_pending = true;
           TR_END(7);   // publish stats, issue residual reads
         }
@@ -523,7 +571,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         const int bytes = p.gather_len * 4;
         for (int off = (pw * 32 + lane) * 128; off < bytes; off += kProducerThreads * 128) prefetch_l2(gin + off);
       }
-      if (ic >= 2) ok = ok && mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((ic >> 1) - 1) & 1, p.status, 22);
+      if (ic >= 2) ok = ok && mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((ic >> 1) - 1) & 1, p.status, 22) &&
+                      mbar_wait(bar(BAR_STAGE_FREE + qbuf), ((ic >> 1) - 1) & 1, p.status, 26);
       if (!ok) return;
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
                           kEs * ((size_t)it.b * p.q_stride[0] + (size_t)it.h * p.q_stride[2]) + chunk_off;
@@ -762,7 +811,7 @@ int num_sms() {
 
 template <int D, int kType>
 int launch(const GatherAttnParams& p, cudaStream_t stream) {
-  using L = Smem<D * (kType == 2 ? 1 : 2)>;
+  using L = Smem<D * (kType == 2 ? 1 : 2), kType == 2 ? 256 * D : 0>;
   auto kern = gather_attn_kernel<D, kType>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return -8;
