@@ -387,6 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     };
 
     bool epi_pending = false;   // the previous item still needs its epilogue
+    bool s_ready = false;       // next tile's score barrier was already complete when probed
 #pragma unroll 1
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
       const Item it = decode_item(p, item);
@@ -397,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       for (int t = 0; t < it.T; ++t, ++g) {
         const int buf = g & 1;
         TR_END(0);
-        ok = mbar_wait(bar(BAR_S_FULL + buf), (g >> 1) & 1, p.status, 10);
+        if (!s_ready) ok = mbar_wait(bar(BAR_S_FULL + buf), (g >> 1) & 1, p.status, 10);
         if (!ok) break;
         tc_fence_after();
         TR_END(1);   // wait S_FULL
@@ -496,6 +497,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         }
         if (!ok) break;
         TR_END(5);   // streaming softmax
+        // probe the next tile's score barrier now, so that a satisfied wait costs nothing at the loop top
+        s_ready = mbar_test_wait(bar(BAR_S_FULL + ((g + 1) & 1)), ((g + 1) >> 1) & 1);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive_relaxed(bar(BAR_P_READY + 2 * x + buf));
@@ -677,13 +680,21 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       TR_BEGIN();
       auto next_slot = [&]() { if (++slot == kRing) { slot = 0; slot_phase ^= 1; } };
 
-      // QK^T of global tile gq (tile t of T of the CTA's ic-th item)
-      auto issue_qk = [&](int gq, int ic, int t, int T) -> bool {
+      // A satisfied mbarrier wait still costs its full latency (a few hundred cycles) when the next
+      // instruction depends on it, and this thread would pay that five times per tile.  So the loop
+      // first probes, back to back and without blocking, every barrier the tile is going to need,
+      // and only falls back to a (bounded) blocking wait for those that were not complete yet.
+      auto wait_if = [&](bool done, uint32_t b, uint32_t parity, int site) -> bool {
+        return done || mbar_wait(b, parity, p.status, site);
+      };
+
+      // QK^T of global tile gq (tile t of T of the CTA's ic-th item); k_ready = probe of the K slot
+      auto issue_qk = [&](int gq, int ic, int t, int T, bool k_ready) -> bool {
         const int qbuf = ic & 1;
         TR_END(0);
         if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) return false;
         TR_END(10);  // wait Q full
-        if (!mbar_wait(bar(BAR_FULL + slot), slot_phase, p.status, 30)) return false;
+        if (!wait_if(k_ready, bar(BAR_FULL + slot), slot_phase, 30)) return false;
         TR_END(1);   // wait K (and Q) full
         fence_proxy_async_smem();
         tc_fence_after();
@@ -706,9 +717,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         next_slot();
         return true;
       };
-      auto issue_pv = [&](int gp, int ic, int t, int T) -> bool {
+      auto issue_pv = [&](int gp, int ic, int t, int T, bool v_ready, bool pa_ready, bool pb_ready) -> bool {
         TR_END(0);
-        if (!mbar_wait(bar(BAR_FULL + slot), slot_phase, p.status, 34)) return false;
+        if (!wait_if(v_ready, bar(BAR_FULL + slot), slot_phase, 34)) return false;
         TR_END(4);   // wait V full
         if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) return false;
         TR_END(5);   // wait O empty
@@ -717,12 +728,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         fence_proxy_async_smem();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (!mbar_wait(bar(BAR_P_READY + 2 * x + buf), (gp >> 1) & 1, p.status, 33)) return false;
+          if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (gp >> 1) & 1, 33)) return false;
           TR_END(6 + x);   // wait P ready (stream x)
           tc_fence_after();
           const uint32_t tP = tmem + kColS + buf * 128 + x * 64;
           const uint32_t tO = tmem + kColO + x * 128;
-#pragma unroll
           if constexpr (kFp8) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -757,17 +767,25 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (q_item < n_items) q_T = decode_item(p, q_item).T;
         }
       };
-      ok = issue_qk(gq, q_ic, q_t, q_T);
+      ok = issue_qk(gq, q_ic, q_t, q_T, false);
       advance_q();
 #pragma unroll 1
       while (ok) {
         const bool have_q = q_item < n_items;
         const int next_T = q_T;
+        // non-blocking probes, issued together: K slot (current ring position), V slot (the one after
+        // it, or the current one if there is no further QK), and both P_READY barriers of tile gp
+        int vslot = slot, vphase = slot_phase;
+        if (have_q && ++vslot == kRing) { vslot = 0; vphase ^= 1; }
+        const bool k_ready = have_q && mbar_test_wait(bar(BAR_FULL + slot), slot_phase);
+        const bool v_ready = mbar_test_wait(bar(BAR_FULL + vslot), vphase);
+        const bool pa_ready = mbar_test_wait(bar(BAR_P_READY + (gp & 1)), (gp >> 1) & 1);
+        const bool pb_ready = mbar_test_wait(bar(BAR_P_READY + 2 + (gp & 1)), (gp >> 1) & 1);
         if (have_q) {
-          ok = issue_qk(gq, q_ic, q_t, q_T);
+          ok = issue_qk(gq, q_ic, q_t, q_T, k_ready);
           if (!ok) break;
         }
-        ok = issue_pv(gp, v_ic, v_t, v_T);
+        ok = issue_pv(gp, v_ic, v_t, v_T, v_ready, pa_ready, pb_ready);
         if (!ok) break;
         ++gp;
         if (++v_t >= v_T) {
