@@ -6,7 +6,7 @@
 // in (head-major, group-minor) order so that the groups in flight at any moment
 // read the K/V of one or two heads, which then stay resident in L2.
 //
-// Roles inside the CTA (416 threads = 13 warps, so that no SM sub-partition hosts more than
+// Roles inside the CTA (448 threads = 14 warps, so that no SM sub-partition hosts more than
 // four warps and every thread can have 128 registers):
 //   warps 0-3   softmax stream A: columns 0-63 of every 128-token KV tile
 //   warps 4-7   softmax stream B: columns 64-127
@@ -20,9 +20,9 @@
 //               completion is signalled by cp.async.mbarrier.arrive.  The row
 //               gather is the scarcest resource of the kernel (measured ceiling about
 //               38 B/clk/SM with four warps issuing), hence the deep ring.
-//   warp 12     MMA issuer (one thread): S = Q K^T into a double-buffered score
-//               tile, O_x += P_x V_x for both streams (P read from tensor memory,
-//               V as an MN-major shared-memory operand).
+//   warp 12     issues S = Q K^T (one thread) into a double-buffered score tile;
+//   warp 13     issues O_x += P_x V_x for both streams (one thread; P read from tensor
+//               memory, V as an MN-major shared-memory operand).
 //
 // Tensor memory (512 columns): score buffers S[0], S[1] (128 columns each; P of a
 // stream overwrites the first 32 columns of its half), O_A, O_B (128 columns each).
@@ -49,7 +49,7 @@ namespace mcs {
 namespace {
 
 constexpr int kTileN = 128;            // KV tokens per tile
-constexpr int kThreads = 416;          // 8 softmax warps + 4 producer warps + 1 MMA warp
+constexpr int kThreads = 448;          // 8 softmax warps + 4 producer warps + 2 MMA-issuing warps
 constexpr int kStreamThreads = 128;
 constexpr int kProducerWarps = 4;
 constexpr int kProducerThreads = kProducerWarps * 32;
@@ -77,7 +77,8 @@ enum {
   BAR_O_EMPTY,
   BAR_STATS,                           // both streams published their (max, sum) of the finished item
   BAR_STAGE_FREE,                      // [2] epilogue staging (= Q buffer of the finished item) released
-  BAR_DRAIN = BAR_STAGE_FREE + 2,
+  BAR_DRAIN = BAR_STAGE_FREE + 2,      // [2] error path of the two issuers
+  BAR_DRAIN_END = BAR_DRAIN + 1,
   BAR_COUNT
 };
 
@@ -230,6 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     mbar_init(bar(BAR_O_EMPTY), 2 * kStreamThreads);
     mbar_init(bar(BAR_STATS), 2 * kStreamThreads);
     mbar_init(bar(BAR_DRAIN), 1);
+    mbar_init(bar(BAR_DRAIN + 1), 1);
     mbar_fence_init();
   }
   if (warp == kMmaWarp) {
@@ -644,6 +646,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           have_k = kc.item < n_items;
           if (have_k) idx_k = load_idx(kc);       // in flight while V(g) is issued
         }
+        if (!had_k) {
+          // no K entry in this (final) step: skip its ring number so that V(g) is always entry 2g+2
+          if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
+        }
         load_tile(vc.kv, v_row, idx_v);
         if (!ok) break;
         idx_v = idx_cur;                           // V(g+1) uses the indices of K(g+1)
@@ -661,75 +667,101 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     TR_FLUSH(2, pw == 0 && lane == 0);
   } else {
     // =====================================================================
-    // MMA issuer: one thread.  tcgen05.mma issue blocks while the (shallow) MMA queue is
-    // full, so every instruction between two MMAs is exposed: descriptors are pre-built
-    // and ring positions are tracked incrementally.
+    // MMA issuers: warp 12 issues every S = Q K^T, warp 13 every O += P V (one thread each).
+    // tcgen05.mma issue blocks while the (shallow) MMA queue is full and every wait, commit and
+    // descriptor computation between two MMAs is exposed latency of the issuing thread; one thread
+    // doing both products needs ~2,300 cycles per tile for 1,000 cycles of tensor work.  Two threads
+    // halve that serial path.  MMAs of different threads are not ordered with respect to each other,
+    // so the one dependency between the two products is explicit: S[buf] holds P of tile g until
+    // P V of tile g has completed, and Q K^T of tile g+2 waits for that (BAR_PV_DONE).
+    // Ring entries are numbered K(0)=0, K(g)=2g-1, V(g)=2g+2 (the producers skip one number before
+    // the very last V), so each issuer steps through its own entries two at a time.
     // =====================================================================
-    if (lane == 0 && blockIdx.x < n_items) {
-      constexpr uint32_t kFmt = (kFp16 || kFp8) ? 0u : 1u;   // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
+    constexpr uint32_t kFmt = (kFp16 || kFp8) ? 0u : 1u;   // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
+    // descriptor high word: stride byte offset 1024, version 1, 128-byte swizzle
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    auto desc = [&](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+    // A satisfied mbarrier wait still costs its full latency when the next instruction depends on it,
+    // so barriers are probed early without blocking and only waited for if they were not complete.
+    auto wait_if = [&](bool done, uint32_t b, uint32_t parity, int site) -> bool {
+      return done || mbar_wait(b, parity, p.status, site);
+    };
+    if (warp == kMmaWarp && lane == 0 && blockIdx.x < n_items) {
+      // ------------------------------------------------------------------ Q K^T issuer
       constexpr uint32_t idesc_qk = mma_idesc(kFmt, kFmt, 0, 0, 128, kTileN);
-      constexpr uint32_t idesc_pv = mma_idesc(kFmt, kFmt, 0, 1, 128, D);
-      // descriptor high word: stride byte offset 1024, version 1, 128-byte swizzle
-      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
       constexpr uint32_t kLboK = (16u >> 4) << 16;       // K-major operands (Q, K): LBO unused
-      constexpr uint32_t kLboV = (16384u >> 4) << 16;    // MN-major V: 16 KB between 64-element column blocks
-      auto desc = [&](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
       bool ok = true;
-      int slot = 0, slot_phase = 0;
+      int slot = 0, phase = 0;                           // ring position of the next K entry
       TR_DECL;
       TR_BEGIN();
-      auto next_slot = [&]() { if (++slot == kRing) { slot = 0; slot_phase ^= 1; } };
-
-      // A satisfied mbarrier wait still costs its full latency (a few hundred cycles) when the next
-      // instruction depends on it, and this thread would pay that five times per tile.  So the loop
-      // first probes, back to back and without blocking, every barrier the tile is going to need,
-      // and only falls back to a (bounded) blocking wait for those that were not complete yet.
-      auto wait_if = [&](bool done, uint32_t b, uint32_t parity, int site) -> bool {
-        return done || mbar_wait(b, parity, p.status, site);
-      };
-
-      // QK^T of global tile gq (tile t of T of the CTA's ic-th item); k_ready = probe of the K slot
-      auto issue_qk = [&](int gq, int ic, int t, int T, bool k_ready) -> bool {
-        const int qbuf = ic & 1;
+      int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
+#pragma unroll 1
+      while (item < n_items) {
+        const int qbuf = ic & 1, buf = g & 1;
+        const bool k_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
+        const bool s_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
         TR_END(0);
-        if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) return false;
-        TR_END(10);  // wait Q full
-        if (!wait_if(k_ready, bar(BAR_FULL + slot), slot_phase, 30)) return false;
+        if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) { ok = false; break; }
+        if (!wait_if(k_ready, bar(BAR_FULL + slot), phase, 30)) { ok = false; break; }
         TR_END(1);   // wait K (and Q) full
+        if (!wait_if(s_free, bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1, 35)) { ok = false; break; }
+        TR_END(4);   // wait score buffer free (P V of tile g-2 done)
         fence_proxy_async_smem();
         tc_fence_after();
-        const uint32_t tS = tmem + kColS + (gq & 1) * 128;
+        const uint32_t tS = tmem + kColS + buf * 128;
         const uint32_t qlo = ((sQ(qbuf) & 0x3FFFFu) >> 4) | kLboK;
         const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboK;
 #pragma unroll
         for (int j = 0; j < RB / 32; ++j) {
           // one k-step = 32 bytes of every row (16 16-bit or 32 8-bit elements) inside the 128-byte swizzle span
-          constexpr uint32_t kStep = 32 >> 4;
-          const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * kStep;
+          const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
           if constexpr (kFp8) mma_f8_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
           else mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
         }
         TR_END(2);   // issue QK MMAs
         tc_commit(bar(BAR_EMPTY + slot));
-        tc_commit(bar(BAR_S_FULL + (gq & 1)));
+        tc_commit(bar(BAR_S_FULL + buf));
         if (t == T - 1) tc_commit(bar(BAR_Q_EMPTY + qbuf));
         TR_END(3);   // QK commits
-        next_slot();
-        return true;
-      };
-      auto issue_pv = [&](int gp, int ic, int t, int T, bool v_ready, bool pa_ready, bool pb_ready) -> bool {
-        TR_END(0);
-        if (!wait_if(v_ready, bar(BAR_FULL + slot), slot_phase, 34)) return false;
-        TR_END(4);   // wait V full
-        if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) return false;
-        TR_END(5);   // wait O empty
-        const int buf = gp & 1;
+        // next K entry: 0 -> 1, then +2
+        const int step = g == 0 ? 1 : 2;
+        slot += step;
+        if (slot >= kRing) { slot -= kRing; phase ^= 1; }
+        ++g;
+        if (++t >= T) {
+          t = 0;
+          item += gridDim.x;
+          ++ic;
+          if (item < n_items) T = decode_item(p, item).T;
+        }
+      }
+      TR_END(0);
+      TR_FLUSH(3, true);
+      if (!ok) {
+        // error path: let outstanding MMAs retire before tensor memory is released
+        tc_commit(bar(BAR_DRAIN));
+        mbar_wait_quiet(bar(BAR_DRAIN), 0, 1 << 20);
+      }
+    } else if (warp == kMmaWarp + 1 && lane == 0 && blockIdx.x < n_items) {
+      // ------------------------------------------------------------------ P V issuer
+      constexpr uint32_t idesc_pv = mma_idesc(kFmt, kFmt, 0, 1, 128, D);
+      constexpr uint32_t kLboV = (16384u >> 4) << 16;    // MN-major V: 16 KB between 64-element column blocks
+      bool ok = true;
+      int slot = 2, phase = 0;                           // ring position of the next V entry (V(0) = entry 2)
+      int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
+#pragma unroll 1
+      while (item < n_items) {
+        const int buf = g & 1;
+        const bool v_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
+        const bool pa_ready = mbar_test_wait(bar(BAR_P_READY + buf), (g >> 1) & 1);
+        const bool pb_ready = mbar_test_wait(bar(BAR_P_READY + 2 + buf), (g >> 1) & 1);
+        if (!wait_if(v_ready, bar(BAR_FULL + slot), phase, 34)) { ok = false; break; }
+        if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) { ok = false; break; }
         const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
         fence_proxy_async_smem();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (gp >> 1) & 1, 33)) return false;
-          TR_END(6 + x);   // wait P ready (stream x)
+          if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (g >> 1) & 1, 33)) { ok = false; break; }
           tc_fence_after();
           const uint32_t tP = tmem + kColS + buf * 128 + x * 64;
           const uint32_t tO = tmem + kColO + x * 128;
@@ -746,62 +778,24 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
               mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (j > 0));
             }
           }
-          TR_END(8);   // issue PV MMAs
         }
+        if (!ok) break;
         tc_commit(bar(BAR_EMPTY + slot));
         tc_commit(bar(BAR_PV_DONE + buf));
         if (t == T - 1) tc_commit(bar(BAR_O_FULL));
-        TR_END(9);   // PV commits
-        next_slot();
-        return true;
-      };
-
-      int q_item = blockIdx.x, q_ic = 0, q_t = 0, q_T = decode_item(p, q_item).T, gq = 0;
-      int v_ic = 0, v_t = 0, v_T = q_T, gp = 0;
-      auto advance_q = [&]() {
-        ++gq;
-        if (++q_t >= q_T) {
-          q_t = 0;
-          q_item += gridDim.x;
-          ++q_ic;
-          if (q_item < n_items) q_T = decode_item(p, q_item).T;
+        slot += 2;
+        if (slot >= kRing) { slot -= kRing; phase ^= 1; }
+        ++g;
+        if (++t >= T) {
+          t = 0;
+          item += gridDim.x;
+          ++ic;
+          if (item < n_items) T = decode_item(p, item).T;
         }
-      };
-      ok = issue_qk(gq, q_ic, q_t, q_T, false);
-      advance_q();
-#pragma unroll 1
-      while (ok) {
-        const bool have_q = q_item < n_items;
-        const int next_T = q_T;
-        // non-blocking probes, issued together: K slot (current ring position), V slot (the one after
-        // it, or the current one if there is no further QK), and both P_READY barriers of tile gp
-        int vslot = slot, vphase = slot_phase;
-        if (have_q && ++vslot == kRing) { vslot = 0; vphase ^= 1; }
-        const bool k_ready = have_q && mbar_test_wait(bar(BAR_FULL + slot), slot_phase);
-        const bool v_ready = mbar_test_wait(bar(BAR_FULL + vslot), vphase);
-        const bool pa_ready = mbar_test_wait(bar(BAR_P_READY + (gp & 1)), (gp >> 1) & 1);
-        const bool pb_ready = mbar_test_wait(bar(BAR_P_READY + 2 + (gp & 1)), (gp >> 1) & 1);
-        if (have_q) {
-          ok = issue_qk(gq, q_ic, q_t, q_T, k_ready);
-          if (!ok) break;
-        }
-        ok = issue_pv(gp, v_ic, v_t, v_T, v_ready, pa_ready, pb_ready);
-        if (!ok) break;
-        ++gp;
-        if (++v_t >= v_T) {
-          if (!have_q) break;
-          v_t = 0;
-          ++v_ic;
-          v_T = next_T;
-        }
-        if (have_q) advance_q();
       }
-      TR_END(0);
-      TR_FLUSH(3, true);
       if (!ok) {
-        // error path: let outstanding MMAs retire before tensor memory is released
-        tc_commit(bar(BAR_DRAIN));
-        mbar_wait_quiet(bar(BAR_DRAIN), 0, 1 << 20);
+        tc_commit(bar(BAR_DRAIN + 1));
+        mbar_wait_quiet(bar(BAR_DRAIN + 1), 0, 1 << 20);
       }
     }
     __syncwarp();
