@@ -10,10 +10,12 @@
 // four warps and every thread can have 128 registers):
 //   warps 0-3   softmax stream A: columns 0-63 of every 128-token KV tile
 //   warps 4-7   softmax stream B: columns 64-127
-//               thread r of a stream owns query row r (= TMEM lane r).  Each
-//               stream keeps its own online-softmax state (row max, row sum)
-//               and its own output accumulator in tensor memory, so the two
-//               halves never exchange anything until the epilogue merges them.
+//               thread r of a stream owns query row r (= TMEM lane r).  The two
+//               threads of a row (warps w and w+4, same SM sub-partition) share one
+//               running row maximum, so both halves of P accumulate into ONE output
+//               accumulator; they agree on it with one two-warp barrier-with-OR per
+//               tile (the maximum itself is exchanged only when it has to be raised),
+//               and keep separate partial row sums that the epilogue adds.
 //   warps 8-11  producers: gather the tile's K rows and V rows with 16-byte
 //               cp.async (16 lanes cover one 256-byte row) into a 5-slot ring of
 //               128-byte-swizzled tiles in the canonical tcgen05 operand layout;
@@ -24,16 +26,21 @@
 //   warp 13     issues O_x += P_x V_x for both streams (one thread; P read from tensor
 //               memory, V as an MN-major shared-memory operand).
 //
-// Tensor memory (512 columns): score buffers S[0], S[1] (128 columns each; P of a
-// stream overwrites the first 32 columns of its half), O_A, O_B (128 columns each).
-// Because S is double-buffered the QK^T of tile g+1 is issued before the softmax
-// of tile g finishes, also across work items (Q is double-buffered in shared
-// memory), so the tensor pipe only waits when softmax falls behind.
+// Tensor memory (512 columns): score buffers S[0], S[1] (128 columns each), probability
+// buffers P[0], P[1] (64 columns each: 32 per stream), O (128 columns).  The dependency
+// chains are kept short and independent:
+//   * a softmax thread copies its 64 scores to registers and releases S[buf] at once, so
+//     Q K^T of tile g+2 only waits for that copy, not for softmax or P V of tile g;
+//   * P has its own buffers, so the softmax of tile g+2 only waits for P V of tile g
+//     (two tiles back) before storing;
+//   * Q is double-buffered in shared memory, so all of this continues across work items.
+// With P aliased onto S (one chain Q K^T -> softmax -> P V -> next Q K^T per buffer) the
+// round trip of about 2,500 cycles of wake-up, commit and MMA latencies per two tiles left
+// the tensor pipe idle most of the time.
 //
-// The epilogue merges the two streams (O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / l),
-// adds the cached dense-minus-sparse residual in fp32, rounds once to the output
-// type and scatters rows back to the original token order when a permutation is
-// given.
+// The epilogue computes O / (l_A + l_B), adds the cached dense-minus-sparse residual in
+// fp32, rounds once to the output type and scatters rows back to the original token
+// order when a permutation is given.
 //
 // Math follows the reference's Hopper kernel
 // (mcsparse/kernels/flash_mcsa/ops/flash_sparse_attn/cute/flash_fwd_sm90.py:1005-1340,
@@ -62,7 +69,8 @@ constexpr int kMmaWarp = 12;
 constexpr int kRing = 5;               // K/V tile slots
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;          // S[buf] at kColS + 128*buf
-constexpr uint32_t kColO = 256;        // O_A at 256, O_B at 384
+constexpr uint32_t kColP = 256;        // P[buf] at kColP + 64*buf; stream x at +32*x
+constexpr uint32_t kColO = 384;        // O
 constexpr int kMaxDynSmem = 232448;    // 227 KB
 
 enum {
@@ -71,8 +79,9 @@ enum {
   BAR_Q_FULL = BAR_EMPTY + kRing,      // [2]
   BAR_Q_EMPTY = BAR_Q_FULL + 2,        // [2]
   BAR_S_FULL = BAR_Q_EMPTY + 2,        // [2] score tile ready
-  BAR_P_READY = BAR_S_FULL + 2,        // [2 streams][2 bufs]
-  BAR_PV_DONE = BAR_P_READY + 4,       // [2] O stable after tile in buf
+  BAR_S_FREE = BAR_S_FULL + 2,         // [2] every softmax thread has copied its scores out of S[buf]
+  BAR_P_READY = BAR_S_FREE + 2,        // [2 streams][2 bufs]
+  BAR_PV_DONE = BAR_P_READY + 4,       // [2] P V of the tile in P[buf] done: P[buf] reusable, O stable
   BAR_O_FULL = BAR_PV_DONE + 2,
   BAR_O_EMPTY,
   BAR_STATS,                           // both streams published their (max, sum) of the finished item
@@ -90,8 +99,9 @@ struct Smem {
   static constexpr int kQ = 0;                           // 2 buffers
   static constexpr int kRingOff = 2 * kTileBytes;
   static constexpr int kBars = kRingOff + kRing * kTileBytes;
-  static constexpr int kStats = kBars + BAR_COUNT * 8;   // float2 [2 streams][128]
-  static constexpr int kTmemSlot = kStats + 2 * 128 * 8;
+  static constexpr int kStats = kBars + BAR_COUNT * 8;   // float [3][128]: partial row sums of streams A, B; row max
+  static constexpr int kXch = kStats + 3 * 128 * 4;      // float [2 streams][128]: tile maxima, exchanged on a raise
+  static constexpr int kTmemSlot = kXch + 2 * 128 * 4;
   // Epilogue staging: 256 rows x (head_dim) bytes of 16-bit output halves.  With 16-bit inputs it is
   // exactly one Q buffer, and the finished item's own Q buffer (idle by then) is used; with 8-bit
   // inputs the Q buffer is half that size and a dedicated area is carved out instead.
@@ -111,7 +121,15 @@ struct Smem {
     if (p.trace != nullptr && blockIdx.x == 0 && (cond))                              \
       for (int tr_i = 0; tr_i < 12; ++tr_i) p.trace[(role) * 16 + tr_i] = tr_acc[tr_i]; \
   } while (0)
+// timeline: clock of event `ev` at CTA-global tile `gg` (tiles TL_FIRST .. TL_FIRST+63 of CTA 0)
+#define TL_FIRST 32
+#define TL(ev, gg, cond)                                                                              \
+  do {                                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && (cond) && (gg) >= TL_FIRST && (gg) < TL_FIRST + 64)  \
+      p.trace[1024 + (ev) * 64 + ((gg) - TL_FIRST)] = clock64();                                      \
+  } while (0)
 #else
+#define TL(ev, gg, cond) do { } while (0)
 #define TR_DECL do { } while (0)
 #define TR_BEGIN() do { } while (0)
 #define TR_END(slot) do { } while (0)
@@ -199,12 +217,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
   const uint32_t s_base = smem_u32(smem);
   const uint32_t bars = s_base + L::kBars;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
-  float2* stats = reinterpret_cast<float2*>(smem + L::kStats);
+  float* stats = reinterpret_cast<float*>(smem + L::kStats);
+  float* xch = reinterpret_cast<float*>(smem + L::kXch);
   auto bar = [&](int i) { return bars + 8u * i; };
   auto sQ = [&](int qb) { return s_base + L::kQ + qb * L::kTileBytes; };
   auto sRing = [&](int slot) { return s_base + L::kRingOff + slot * L::kTileBytes; };
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // provably warp-uniform
   const int n_items = p.B * p.H * p.M;
 
   if (static_cast<int>(smem - smem_raw) + L::kTotal > L::kDynamic) {
@@ -222,6 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       mbar_init(bar(BAR_Q_FULL + i), kProducerThreads);
       mbar_init(bar(BAR_Q_EMPTY + i), 1);
       mbar_init(bar(BAR_S_FULL + i), 1);
+      mbar_init(bar(BAR_S_FREE + i), 2 * kStreamThreads);
       mbar_init(bar(BAR_P_READY + i), kStreamThreads);
       mbar_init(bar(BAR_P_READY + 2 + i), kStreamThreads);
       mbar_init(bar(BAR_PV_DONE + i), 1);
@@ -250,7 +271,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     const int x = warp >> 2;                       // stream 0 (A) or 1 (B)
     const int r_in = (warp & 3) * 32 + lane;       // row inside the group
     const uint32_t lane_addr = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
-    const uint32_t tOx = tmem + kColO + x * 128 + lane_addr;
     float scale_log2 = p.scale_log2;
     // Lazy rescale: the running max is only raised (and O rescaled) when a tile's max exceeds
     // it by more than kRescale log2 units, so P stays <= 2^(kRescale + kBias): far inside the
@@ -267,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     TR_BEGIN();
 
     // ---- epilogue of a finished item, for this thread's row and this stream's half of the output
-    // columns: O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / l + residual, rounded once to the output type and
+    // columns: O / (l_A + l_B) + residual, rounded once to the output type and
     // written to the row's original position.  It is deferred: the residual reads are issued while
     // the item's last tile is being processed, and the rest runs after the first tile of the NEXT
     // item, when the item's last P V has long completed, so the softmax threads never sit idle
@@ -329,23 +349,19 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (!mbar_wait(bar(BAR_O_FULL), eic & 1, p.status, 11)) return false;
       if (!mbar_wait(bar(BAR_STATS), eic & 1, p.status, 14)) return false;
       tc_fence_after();
-      const float2 sa = stats[r_in], sb = stats[128 + r_in];
-      const float m_all = fmaxf(sa.x, sb.x);
-      const float fa = ex2_approx(sa.x - m_all), fb = ex2_approx(sb.x - m_all);
-      const float l_all = sa.y * fa + sb.y * fb;
-      const float inv_l = 1.f / l_all;
-      const float wa = fa * inv_l * epi.vscale, wb = fb * inv_l * epi.vscale;
-      const uint32_t tOa = tmem + kColO + x * kHalf + lane_addr;
-      const uint32_t tOb = tmem + kColO + 128 + x * kHalf + lane_addr;
+      // both streams' partial sums are relative to the same (shared) row maximum
+      const float m_all = stats[256 + r_in];
+      const float l_all = stats[r_in] + stats[128 + r_in];
+      const float w = epi.vscale / l_all;
+      const uint32_t tO = tmem + kColO + x * kHalf + lane_addr;
       const uint32_t st = stage_of(eic);
       const uint32_t my_row = st + lane * kHalfBytes;
       cp_async_wait_all();
       __syncwarp();
 #pragma unroll
       for (int c = 0; c < kHalf / 16; ++c) {
-        uint32_t ra[16], rb[16];
-        tmem_ld16(tOa + c * 16, ra);
-        tmem_ld16(tOb + c * 16, rb);
+        uint32_t ra[16];
+        tmem_ld16(tO + c * 16, ra);
         tmem_wait_ld();
         if (c == kHalf / 16 - 1) {
           // all of this thread's reads of O and of the statistics are done
@@ -363,8 +379,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           for (int j = 0; j < 4; ++j) {
             const float2 rr = unpack16<kFp16>(rw[j]);
             const int k = q4 * 8 + 2 * j;
-            const float o0 = fmaf(__uint_as_float(ra[k]), wa, fmaf(__uint_as_float(rb[k]), wb, rr.x));
-            const float o1 = fmaf(__uint_as_float(ra[k + 1]), wa, fmaf(__uint_as_float(rb[k + 1]), wb, rr.y));
+            const float o0 = fmaf(__uint_as_float(ra[k]), w, rr.x);
+            const float o1 = fmaf(__uint_as_float(ra[k + 1]), w, rr.y);
             ow[j] = pack16<kFp16>(o0, o1);
           }
           sts_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
@@ -390,12 +406,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 
     bool epi_pending = false;   // the previous item still needs its epilogue
     bool s_ready = false;       // next tile's score barrier was already complete when probed
+    const int pair_bar = 1 + (warp & 3);            // named barrier of this row block's two warps (w, w+4)
+    const uint32_t tOh = tmem + kColO + x * kHalf + lane_addr;   // this thread's half of its output row
 #pragma unroll 1
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
       const Item it = decode_item(p, item);
       if (kFp8) scale_log2 = p.scale_qk_log2[item];
-      float m_run = -INFINITY;   // running (possibly stale) row max, log2 domain
-      float l_run = 0.f;         // running row sum relative to m_run
+      float m_run = -INFINITY;   // running (possibly stale) row max, log2 domain; identical in both streams
+      float l_run = 0.f;         // this stream's partial row sum relative to m_run
 #pragma unroll 1
       for (int t = 0; t < it.T; ++t, ++g) {
         const int buf = g & 1;
@@ -404,107 +422,110 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         if (!ok) break;
         tc_fence_after();
         TR_END(1);   // wait S_FULL
+        TL(x == 0 ? 7 : 10, g, lane == 0 && (warp & 3) == 0);
+        // Copy this thread's 64 scores to registers and hand S[buf] back to the Q K^T issuer at once.
         const uint32_t tSx = tmem + kColS + buf * 128 + x * 64 + lane_addr;
-        // Streaming online softmax over this stream's 64 score columns, 32 at a time: chunk max,
-        // lazy raise of the running max (rare), exp2, row sum, pack, store P.  P chunk q (16 packed
-        // columns at 16q) only overwrites score columns that were already read (chunk q sits at 32q).
+        uint32_t sc[64];
+        tmem_ld32(tSx, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
+        tmem_ld32(tSx + 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive_relaxed(bar(BAR_S_FREE + buf));
+        TL(8, g, x == 0 && lane == 0 && (warp & 3) == 0);
+        // P[buf] was last read by P V of tile g-2: probe now, wait (if at all) just before the stores
+        const bool p_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
+        TR_END(2);   // tmem ld
+        // four independent chains of three-input maxima
+        float mx0 = fmaxf(__uint_as_float(sc[0]), __uint_as_float(sc[1]));
+        float mx1 = fmaxf(__uint_as_float(sc[2]), __uint_as_float(sc[3]));
+        float mx2 = fmaxf(__uint_as_float(sc[4]), __uint_as_float(sc[5]));
+        float mx3 = fmaxf(__uint_as_float(sc[6]), __uint_as_float(sc[7]));
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          uint32_t sc[32];
-          tmem_ld32(tSx + q * 32, sc);
-          tmem_wait_ld();
-          TR_END(2);   // tmem ld
-          float mx0 = fmaxf(__uint_as_float(sc[0]), __uint_as_float(sc[1]));
-          float mx1 = fmaxf(__uint_as_float(sc[2]), __uint_as_float(sc[3]));
-          float mx2 = fmaxf(__uint_as_float(sc[4]), __uint_as_float(sc[5]));
-          float mx3 = fmaxf(__uint_as_float(sc[6]), __uint_as_float(sc[7]));
-#pragma unroll
-          for (int i = 8; i < 32; i += 8) {
-            mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])));
-            mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3])));
-            mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5])));
-            mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7])));
-          }
-          const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
-          const bool need = (m_new - m_run) > kRescale;       // always true for the first chunk of an item
-          if (__any_sync(0xffffffffu, need)) {
-            // Raise the running max: everything accumulated relative to the old max is multiplied
-            // by alpha = 2^(old - new): the row sum, the P chunk of this tile written so far and,
-            // from the second tile on, the output accumulator (stable once the previous P V is done).
-            const float alpha = need ? ex2_approx(m_run - m_new) : 1.f;
-            if (need) m_run = m_new;
-            l_run *= alpha;
-            if (t > 0) {
-              ok = mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, p.status, 12);
-              if (!ok) break;
-              tc_fence_after();
+        for (int i = 8; i < 64; i += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sc[i + 2]), __uint_as_float(sc[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sc[i + 4]), __uint_as_float(sc[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sc[i + 6]), __uint_as_float(sc[i + 7]));
+        }
+        const float m_loc = fmaxf(fmax3(mx0, mx1, mx2), mx3) * scale_log2;
+        // Lazy raise of the shared running max.  One barrier-with-OR per tile between the two warps of
+        // this row block tells both whether any of their 64 threads wants a raise (always at the first
+        // tile of an item, rarely afterwards); only then are the tile maxima exchanged.
+        const bool want = (m_loc - m_run) > kRescale;
+        if (named_bar_red_or(pair_bar, 64, want)) {
+          xch[x * 128 + r_in] = m_loc;
+          named_bar_sync(pair_bar, 64);
+          const float m_new = fmaxf(m_loc, xch[(x ^ 1) * 128 + r_in]);
+          const bool raise = (m_new - m_run) > kRescale;      // the same decision in both threads of the row
+          // everything accumulated relative to the old max is multiplied by alpha = 2^(old - new):
+          // the partial row sum and, from the second tile on, this thread's half of the output row
+          // (stable once the previous P V is done)
+          const float alpha = raise ? ex2_approx(m_run - m_new) : 1.f;
+          if (raise) m_run = m_new;
+          l_run *= alpha;
+          if (t > 0) {
+            ok = mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, p.status, 12);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll 1
-              for (int c = 0; c < D / 8; ++c) {
-                uint32_t r[8];
-                tmem_ld8(tOx + c * 8, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                tmem_st8(tOx + c * 8, r);
-              }
-            }
-#pragma unroll 1
-            for (int c = 0; c < (kFp8 ? q : 2 * q); ++c) {      // 8 columns = 16 (16-bit) or 32 (8-bit) values
+            for (int c = 0; c < kHalf / 8; ++c) {
               uint32_t r[8];
-              tmem_ld8(tSx + c * 8, r);
+              tmem_ld8(tOh + c * 8, r);
               tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                if constexpr (kFp8) {
-                  float f[4];
-                  unpack_e4m3x4(r[i], f);
-                  r[i] = pack_e4m3x4(f[0] * alpha, f[1] * alpha, f[2] * alpha, f[3] * alpha);
-                } else {
-                  const float2 f = unpack16<kFp16>(r[i]);
-                  r[i] = pack16<kFp16>(f.x * alpha, f.y * alpha);
-                }
-              }
-              tmem_st8(tSx + c * 8, r);
+              for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st8(tOh + c * 8, r);
             }
-            TR_END(4);   // rescale (rare)
           }
-          const float neg_m = kBias - m_run;
-          float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-          uint32_t pk8[8];       // e4m3 only: the chunk's 32 values
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            uint32_t pk[8];
-#pragma unroll
-            for (int i = 0; i < 8; i += 2) {
-              const int e = h2 * 16 + 2 * i;
-              const float p0 = ex2_approx(fmaf(__uint_as_float(sc[e]), scale_log2, neg_m));
-              const float p1 = ex2_approx(fmaf(__uint_as_float(sc[e + 1]), scale_log2, neg_m));
-              const float p2 = ex2_approx(fmaf(__uint_as_float(sc[e + 2]), scale_log2, neg_m));
-              const float p3 = ex2_approx(fmaf(__uint_as_float(sc[e + 3]), scale_log2, neg_m));
-              ls0 += p0;
-              ls1 += p1;
-              ls2 += p2;
-              ls3 += p3;
-              if constexpr (kFp8) {
-                pk8[h2 * 4 + i / 2] = pack_e4m3x4(p0, p1, p2, p3);
-              } else {
-                pk[i] = pack16<kFp16>(p0, p1);
-                pk[i + 1] = pack16<kFp16>(p2, p3);
-              }
-            }
-            if constexpr (!kFp8) tmem_st8(tSx + q * 16 + h2 * 8, pk);
-          }
-          if constexpr (kFp8) tmem_st8(tSx + q * 8, pk8);
-          l_run += (ls0 + ls1) + (ls2 + ls3);
+          TR_END(4);   // raise (rare)
         }
+        const float neg_m = kBias - m_run;
+        TL(17, g, x == 0 && lane == 0 && (warp & 3) == 0);
+        if (!p_free) ok = mbar_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1, p.status, 15);
         if (!ok) break;
-        TR_END(5);   // streaming softmax
+        TL(18, g, x == 0 && lane == 0 && (warp & 3) == 0);
+        // exp2, partial row sum, pack, store P: 16 values (8 or 4 columns) at a time
+        const uint32_t tPx = tmem + kColP + buf * 64 + x * 32 + lane_addr;
+        float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+        uint32_t pk8[8];       // e4m3 only: two groups of 16 values share one store
+#pragma unroll
+        for (int h4 = 0; h4 < 4; ++h4) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) {
+            const int e = h4 * 16 + 2 * i;
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sc[e]), scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sc[e + 1]), scale_log2, neg_m));
+            const float p2 = ex2_approx(fmaf(__uint_as_float(sc[e + 2]), scale_log2, neg_m));
+            const float p3 = ex2_approx(fmaf(__uint_as_float(sc[e + 3]), scale_log2, neg_m));
+            ls0 += p0;
+            ls1 += p1;
+            ls2 += p2;
+            ls3 += p3;
+            if constexpr (kFp8) {
+              pk8[(h4 & 1) * 4 + i / 2] = pack_e4m3x4(p0, p1, p2, p3);
+            } else {
+              pk[i] = pack16<kFp16>(p0, p1);
+              pk[i + 1] = pack16<kFp16>(p2, p3);
+            }
+          }
+          if constexpr (kFp8) {
+            if (h4 & 1) tmem_st8(tPx + (h4 >> 1) * 8, pk8);      // 32 e4m3 values = 8 columns
+          } else {
+            tmem_st8(tPx + h4 * 8, pk);                         // 16 16-bit values = 8 columns
+          }
+        }
+        l_run += (ls0 + ls1) + (ls2 + ls3);
+        TR_END(5);   // softmax
+        TL(19, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // probe the next tile's score barrier now, so that a satisfied wait costs nothing at the loop top
         s_ready = mbar_test_wait(bar(BAR_S_FULL + ((g + 1) & 1)), ((g + 1) >> 1) & 1);
         tmem_wait_st();
+        TL(20, g, x == 0 && lane == 0 && (warp & 3) == 0);
         tc_fence_before();
         mbar_arrive_relaxed(bar(BAR_P_READY + 2 * x + buf));
         TR_END(6);   // st + arrive
+        TL(x == 0 ? 9 : 11, g, lane == 0 && (warp & 3) == 0);
         if (t == 0 && epi_pending) {
           // the previous item's last P V completed long ago: finish it now
           ok = epilogue_finish(ic - 1);
@@ -520,7 +541,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
           if (!ok) break;
           TR_END(9);   // wait previous O_EMPTY
-          stats[x * 128 + r_in] = make_float2(m_run, l_run);
+          stats[x * 128 + r_in] = l_run;
+          if (x == 0) stats[256 + r_in] = m_run;
           mbar_arrive(bar(BAR_STATS));
           TR_END(10);  // stats store + arrive
           epilogue_prepare(it, ic);
@@ -585,15 +607,20 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       cp_async_arrive_noinc(bar(BAR_Q_FULL + qbuf));
     };
 
-    auto load_tile = [&](const uint8_t* lane_src, size_t row_bytes, int idx) {
+    int tl_k = 0, tl_v = 0;   // diagnostics: CTA-global tile numbers of the K and V cursors
+    (void)tl_k; (void)tl_v;
+    auto load_tile = [&](const uint8_t* lane_src, size_t row_bytes, int idx, bool is_v) {
       TR_END(0);
       if (wrapped) ok = ok && mbar_wait(bar(BAR_EMPTY + slot), slot_phase ^ 1, p.status, 20);
       if (!ok) return;
       TR_END(1);   // wait for a free ring slot
+      TL(is_v ? 14 : 12, is_v ? tl_v : tl_k, pw == 0 && lane == 0);
       // raw index, clamped only here: the global load issued one step earlier stays in flight until now
       warp_gather_rows<RB>(sRing(slot), row0, min(max(idx, 0), p.Sk - 1), lane_src, row_bytes, lane);
       cp_async_arrive_noinc(bar(BAR_FULL + slot));
       TR_END(2);   // issue the tile's cp.async
+      TL(is_v ? 15 : 13, is_v ? tl_v : tl_k, pw == 0 && lane == 0);
+      if (is_v) ++tl_v; else ++tl_k;
       if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
     };
 
@@ -620,7 +647,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       set_item(vc, p.v, p.v_stride);
       enter_item(kc.item, kc.ic);
       int idx_k = load_idx(kc);
-      load_tile(kc.kv, k_row, idx_k);
+      load_tile(kc.kv, k_row, idx_k, false);
       int idx_v = idx_k;
       auto advance_k = [&]() {
         if (++kc.t >= kc.T) {
@@ -640,7 +667,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         if (had_k) {
           if (kc.t == 0) enter_item(kc.item, kc.ic);
           if (!ok) break;
-          load_tile(kc.kv, k_row, idx_cur);
+          load_tile(kc.kv, k_row, idx_cur, false);
           if (!ok) break;
           advance_k();
           have_k = kc.item < n_items;
@@ -650,7 +677,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           // no K entry in this (final) step: skip its ring number so that V(g) is always entry 2g+2
           if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
         }
-        load_tile(vc.kv, v_row, idx_v);
+        load_tile(vc.kv, v_row, idx_v, true);
         if (!ok) break;
         idx_v = idx_cur;                           // V(g+1) uses the indices of K(g+1)
         if (++vc.t >= vc.T) {
@@ -667,13 +694,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     TR_FLUSH(2, pw == 0 && lane == 0);
   } else {
     // =====================================================================
-    // MMA issuers: warp 12 issues every S = Q K^T, warp 13 every O += P V (one thread each).
-    // tcgen05.mma issue blocks while the (shallow) MMA queue is full and every wait, commit and
-    // descriptor computation between two MMAs is exposed latency of the issuing thread; one thread
-    // doing both products needs ~2,300 cycles per tile for 1,000 cycles of tensor work.  Two threads
-    // halve that serial path.  MMAs of different threads are not ordered with respect to each other,
-    // so the one dependency between the two products is explicit: S[buf] holds P of tile g until
-    // P V of tile g has completed, and Q K^T of tile g+2 waits for that (BAR_PV_DONE).
+    // MMA issuers: warp 12 issues every S = Q K^T, warp 13 every O += P V.  Both warps run their
+    // loops converged on warp-uniform values; one elected lane executes the tcgen05 instructions.
+    // The MMA queue holds about five 128x128x16 products, so whatever an issuer does between two
+    // bursts (waits, commits, bookkeeping) has to fit into about 300 cycles or the tensor pipe drains;
+    // two issuers keep each other's gaps covered.  The two products share no tensor-memory buffer (P has its own), so
+    // the issuers never wait for each other: Q K^T of tile g+2 waits for the softmax threads'
+    // register copy of S[buf] (BAR_S_FREE), P V of tile g for P (BAR_P_READY) and V.
     // Ring entries are numbered K(0)=0, K(g)=2g-1, V(g)=2g+2 (the producers skip one number before
     // the very last V), so each issuer steps through its own entries two at a time.
     // =====================================================================
@@ -686,7 +713,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     auto wait_if = [&](bool done, uint32_t b, uint32_t parity, int site) -> bool {
       return done || mbar_wait(b, parity, p.status, site);
     };
-    if (warp == kMmaWarp && lane == 0 && blockIdx.x < n_items) {
+    const bool leader = elect_one();
+    if (warp == kMmaWarp && blockIdx.x < n_items) {
       // ------------------------------------------------------------------ Q K^T issuer
       constexpr uint32_t idesc_qk = mma_idesc(kFmt, kFmt, 0, 0, 128, kTileN);
       constexpr uint32_t kLboK = (16u >> 4) << 16;       // K-major operands (Q, K): LBO unused
@@ -698,16 +726,18 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 #pragma unroll 1
       while (item < n_items) {
         const int qbuf = ic & 1, buf = g & 1;
+        TL(16, g, lane == 0);
         const bool k_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
-        const bool s_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
+        const bool s_free = g < 2 || mbar_test_wait(bar(BAR_S_FREE + buf), ((g >> 1) - 1) & 1);
         TR_END(0);
         if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) { ok = false; break; }
         if (!wait_if(k_ready, bar(BAR_FULL + slot), phase, 30)) { ok = false; break; }
         TR_END(1);   // wait K (and Q) full
-        if (!wait_if(s_free, bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1, 35)) { ok = false; break; }
-        TR_END(4);   // wait score buffer free (P V of tile g-2 done)
+        if (!wait_if(s_free, bar(BAR_S_FREE + buf), ((g >> 1) - 1) & 1, 35)) { ok = false; break; }
+        TR_END(4);   // wait score buffer free (softmax of tile g-2 has copied its scores out)
         fence_proxy_async_smem();
         tc_fence_after();
+        TL(0, g, lane == 0);
         const uint32_t tS = tmem + kColS + buf * 128;
         const uint32_t qlo = ((sQ(qbuf) & 0x3FFFFu) >> 4) | kLboK;
         const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboK;
@@ -715,14 +745,20 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         for (int j = 0; j < RB / 32; ++j) {
           // one k-step = 32 bytes of every row (16 16-bit or 32 8-bit elements) inside the 128-byte swizzle span
           const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
-          if constexpr (kFp8) mma_f8_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
-          else mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+          if (leader) {
+            if constexpr (kFp8) mma_f8_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+            else mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+          }
         }
         TR_END(2);   // issue QK MMAs
-        tc_commit(bar(BAR_EMPTY + slot));
-        tc_commit(bar(BAR_S_FULL + buf));
-        if (t == T - 1) tc_commit(bar(BAR_Q_EMPTY + qbuf));
+        TL(1, g, lane == 0);
+        if (leader) {
+          tc_commit(bar(BAR_EMPTY + slot));
+          tc_commit(bar(BAR_S_FULL + buf));
+          if (t == T - 1) tc_commit(bar(BAR_Q_EMPTY + qbuf));
+        }
         TR_END(3);   // QK commits
+        TL(2, g, lane == 0);
         // next K entry: 0 -> 1, then +2
         const int step = g == 0 ? 1 : 2;
         slot += step;
@@ -736,53 +772,66 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         }
       }
       TR_END(0);
-      TR_FLUSH(3, true);
+      TR_FLUSH(3, lane == 0);
       if (!ok) {
         // error path: let outstanding MMAs retire before tensor memory is released
-        tc_commit(bar(BAR_DRAIN));
+        if (leader) tc_commit(bar(BAR_DRAIN));
         mbar_wait_quiet(bar(BAR_DRAIN), 0, 1 << 20);
       }
-    } else if (warp == kMmaWarp + 1 && lane == 0 && blockIdx.x < n_items) {
+    } else if (warp == kMmaWarp + 1 && blockIdx.x < n_items) {
       // ------------------------------------------------------------------ P V issuer
       constexpr uint32_t idesc_pv = mma_idesc(kFmt, kFmt, 0, 1, 128, D);
       constexpr uint32_t kLboV = (16384u >> 4) << 16;    // MN-major V: 16 KB between 64-element column blocks
       bool ok = true;
       int slot = 2, phase = 0;                           // ring position of the next V entry (V(0) = entry 2)
       int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
+      TR_DECL;
+      TR_BEGIN();
 #pragma unroll 1
       while (item < n_items) {
         const int buf = g & 1;
+        TR_END(0);
+        TL(3, g, lane == 0);
         const bool v_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
         const bool pa_ready = mbar_test_wait(bar(BAR_P_READY + buf), (g >> 1) & 1);
         const bool pb_ready = mbar_test_wait(bar(BAR_P_READY + 2 + buf), (g >> 1) & 1);
         if (!wait_if(v_ready, bar(BAR_FULL + slot), phase, 34)) { ok = false; break; }
         if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) { ok = false; break; }
+        TR_END(1);   // wait V (and O_EMPTY)
         const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
         fence_proxy_async_smem();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (g >> 1) & 1, 33)) { ok = false; break; }
+          TR_END(2);   // wait P
+          if (x == 0) TL(4, g, lane == 0);
           tc_fence_after();
-          const uint32_t tP = tmem + kColS + buf * 128 + x * 64;
-          const uint32_t tO = tmem + kColO + x * 128;
+          const uint32_t tP = tmem + kColP + buf * 64 + x * 32;
+          const uint32_t tO = tmem + kColO;
           if constexpr (kFp8) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               // A: 32 e4m3 values = 8 TMEM columns per k-step; B: 32 KV rows of 128 bytes = 4096 bytes
-              mma_f8_ts(tO, tP + j * 8, desc(vlo + (x * 2 + j) * (4096 >> 4)), idesc_pv, (t > 0) || (j > 0));
+              if (leader) mma_f8_ts(tO, tP + j * 8, desc(vlo + (x * 2 + j) * (4096 >> 4)), idesc_pv, (t > 0) || (x > 0) || (j > 0));
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               // A: 16 packed 16-bit values = 8 TMEM columns per k-step; B: 16 KV rows = 2048 bytes
-              mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (j > 0));
+              if (leader) mma_f16_ts(tO, tP + j * 8, desc(vlo + (x * 4 + j) * (2048 >> 4)), idesc_pv, (t > 0) || (x > 0) || (j > 0));
             }
           }
         }
         if (!ok) break;
-        tc_commit(bar(BAR_EMPTY + slot));
-        tc_commit(bar(BAR_PV_DONE + buf));
-        if (t == T - 1) tc_commit(bar(BAR_O_FULL));
+        TR_END(3);   // issue PV MMAs
+        TL(5, g, lane == 0);
+        if (leader) {
+          tc_commit(bar(BAR_EMPTY + slot));
+          tc_commit(bar(BAR_PV_DONE + buf));
+          if (t == T - 1) tc_commit(bar(BAR_O_FULL));
+        }
+        TR_END(4);   // PV commits
+        TL(6, g, lane == 0);
         slot += 2;
         if (slot >= kRing) { slot -= kRing; phase ^= 1; }
         ++g;
@@ -793,8 +842,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (item < n_items) T = decode_item(p, item).T;
         }
       }
+      TR_FLUSH(4, lane == 0);
       if (!ok) {
-        tc_commit(bar(BAR_DRAIN + 1));
+        if (leader) tc_commit(bar(BAR_DRAIN + 1));
         mbar_wait_quiet(bar(BAR_DRAIN + 1), 0, 1 << 20);
       }
     }
