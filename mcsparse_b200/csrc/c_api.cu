@@ -12,7 +12,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
-#ifdef MCS_TRACE
+#if defined(MCS_TRACE) || defined(MCS_CLK)
 static long long* g_trace = nullptr;
 extern "C" void mcs_debug_set_trace(long long* t) { g_trace = t; }
 #endif
@@ -72,7 +72,7 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.H = a->H; p.D = a->D;
   p.M = (int)groups; p.gather_len = a->gather_len; p.group_rows = a->group_rows;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#ifdef MCS_TRACE
+#if defined(MCS_TRACE) || defined(MCS_CLK)
   p.trace = g_trace;
 #endif
 

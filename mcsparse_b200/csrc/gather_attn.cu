@@ -6,8 +6,8 @@
 // in (head-major, group-minor) order so that the groups in flight at any moment
 // read the K/V of one or two heads, which then stay resident in L2.
 //
-// Roles inside the CTA (448 threads = 14 warps, so that no SM sub-partition hosts more than
-// four warps and every thread can have 128 registers):
+// Roles inside the CTA (576 threads = 18 warps; the two SM sub-partitions that host five warps
+// limit every thread to 96 registers):
 //   warps 0-3   softmax stream A: columns 0-63 of every 128-token KV tile
 //   warps 4-7   softmax stream B: columns 64-127
 //               thread r of a stream owns query row r (= TMEM lane r).  The two
@@ -22,9 +22,13 @@
 //               completion is signalled by cp.async.mbarrier.arrive.  The row
 //               gather is the scarcest resource of the kernel (measured ceiling about
 //               38 B/clk/SM with four warps issuing), hence the deep ring.
-//   warp 12     issues S = Q K^T (one thread) into a double-buffered score tile;
-//   warp 13     issues O_x += P_x V_x for both streams (one thread; P read from tensor
-//               memory, V as an MN-major shared-memory operand).
+//   warp 12     issues S = Q K^T into a double-buffered score tile;
+//   warp 13     issues O += P_x V_x for both streams (P read from tensor memory, V as an
+//               MN-major shared-memory operand).  Both run converged; one elected lane
+//               executes the tcgen05 instructions.
+//   warps 14-17 epilogue: one warp per tensor-memory lane group copies the finished O out,
+//               normalises, adds the residual and writes the rows, while the other roles are
+//               already working on the next item.
 //
 // Tensor memory (512 columns): score buffers S[0], S[1] (128 columns each), probability
 // buffers P[0], P[1] (64 columns each: 32 per stream), O (128 columns).  The dependency
@@ -56,16 +60,17 @@ namespace mcs {
 namespace {
 
 constexpr int kTileN = 128;            // KV tokens per tile
-constexpr int kThreads = 448;          // 8 softmax warps + 4 producer warps + 2 MMA-issuing warps
-constexpr int kStreamThreads = 128;
+constexpr int kThreads = 576;          // 8 softmax + 4 producer + 2 MMA-issuing + 4 epilogue warps
+constexpr int kSoftmaxWarps = 8;
 constexpr int kProducerWarps = 4;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kRowsPerProducerWarp = 128 / kProducerWarps;
 constexpr int kProducerWarp0 = 8;
 constexpr int kMmaWarp = 12;
-// All 13 warps run with the same 128-register budget (no setmaxnreg: with a partial fourth
-// warpgroup its hand-over never completed on this part).  The softmax loop is written as a
-// streaming pass over 16 score columns at a time so that it needs about half of that.
+constexpr int kEpiWarp0 = 14;           // warps 14-17: lane groups 2, 3, 0, 1
+constexpr int kEpiWarps = 4;
+// All warps run with the same register budget (no setmaxnreg: with a partial last warpgroup its
+// hand-over never completed on this part).
 constexpr int kRing = 5;               // K/V tile slots
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;          // S[buf] at kColS + 128*buf
@@ -242,15 +247,15 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       mbar_init(bar(BAR_Q_FULL + i), kProducerThreads);
       mbar_init(bar(BAR_Q_EMPTY + i), 1);
       mbar_init(bar(BAR_S_FULL + i), 1);
-      mbar_init(bar(BAR_S_FREE + i), 2 * kStreamThreads);
-      mbar_init(bar(BAR_P_READY + i), kStreamThreads);
-      mbar_init(bar(BAR_P_READY + 2 + i), kStreamThreads);
+      mbar_init(bar(BAR_S_FREE + i), kSoftmaxWarps);
+      mbar_init(bar(BAR_P_READY + i), kSoftmaxWarps / 2);
+      mbar_init(bar(BAR_P_READY + 2 + i), kSoftmaxWarps / 2);
       mbar_init(bar(BAR_PV_DONE + i), 1);
-      mbar_init(bar(BAR_STAGE_FREE + i), 2 * kStreamThreads);
+      mbar_init(bar(BAR_STAGE_FREE + i), kEpiWarps);
     }
     mbar_init(bar(BAR_O_FULL), 1);
-    mbar_init(bar(BAR_O_EMPTY), 2 * kStreamThreads);
-    mbar_init(bar(BAR_STATS), 2 * kStreamThreads);
+    mbar_init(bar(BAR_O_EMPTY), kEpiWarps);
+    mbar_init(bar(BAR_STATS), kSoftmaxWarps);
     mbar_init(bar(BAR_DRAIN), 1);
     mbar_init(bar(BAR_DRAIN + 1), 1);
     mbar_fence_init();
@@ -268,6 +273,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     // =====================================================================
     // softmax streams: thread == query row == TMEM lane
     // =====================================================================
+    // One arrival per warp: an mbarrier arrive is a shared-memory atomic, the 32 lanes of a warp
+    // arriving on the same barrier are serialised, and per-thread arrivals cost the CTA hundreds of
+    // serialised atomics per tile.  Every lane has finished (and fenced) its part before __syncwarp.
+    auto warp_arrive = [&](uint32_t b) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b);
+    };
     const int x = warp >> 2;                       // stream 0 (A) or 1 (B)
     const int r_in = (warp & 3) * 32 + lane;       // row inside the group
     const uint32_t lane_addr = (static_cast<uint32_t>(warp & 3) * 32u) << 16;
@@ -285,126 +297,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     bool ok = true;
     TR_DECL;
     TR_BEGIN();
+#if defined(MCS_CLK)
+    // diagnostics: SM clocks and nanoseconds this role of CTA 0 ran (the SM clock under load)
+    const long long clk_c0 = clock64();
+    const unsigned long long clk_g0 = globaltimer_ns();
+#endif
 
-    // ---- epilogue of a finished item, for this thread's row and this stream's half of the output
-    // columns: O / (l_A + l_B) + residual, rounded once to the output type and
-    // written to the row's original position.  It is deferred: the residual reads are issued while
-    // the item's last tile is being processed, and the rest runs after the first tile of the NEXT
-    // item, when the item's last P V has long completed, so the softmax threads never sit idle
-    // waiting for the tensor pipe, and never wait for a global load.
-    constexpr int kHalf = D / 2;                 // output columns handled by this stream
-    struct Epi {
-      uint8_t* out;          // this row's output + column offset, or null for a padding row
-      const uint8_t* res;    // residual row + column offset, or null
-      float* lse;            // stream A only, or null
-      float vscale;          // e4m3: scale_v[b,h]; else 1
-    };
-    Epi epi{nullptr, nullptr, nullptr, 1.f};
-    // Global traffic of the epilogue is staged through shared memory so that every global access is
-    // coalesced (8 or 4 lanes per 128/64-byte half row): a thread owns a ROW in tensor memory, and 32
-    // row-strided 16-byte accesses per instruction cost the load/store unit 32 wavefronts each.
-    // Each warp has a private 32-row area, XOR-swizzled by row so that both access patterns are
-    // conflict-free.  The residual is brought in with cp.async right after the item's last tile.
-    constexpr int kHalfBytes = kHalf * 2;                 // bytes of this stream's half of an output row
-    constexpr int kCh = kHalfBytes / 16;                  // 16-byte chunks per half row
-    constexpr int kRpi = 32 / kCh;                        // rows covered by one coalesced warp access
-    auto stage_of = [&](int eic) -> uint32_t {
-      const uint32_t base = kFp8 ? (s_base + L::kStage) : sQ(eic & 1);
-      return base + static_cast<uint32_t>(warp) * 32u * kHalfBytes;
-    };
-    bool epi_has_res = false;
-    auto epilogue_prepare = [&](const Item& it, int eic) {
-      epi = Epi{nullptr, nullptr, nullptr, kFp8 ? p.scale_v[it.bh] : 1.f};
-      if (r_in < it.rows_valid) {
-        const int row = it.row_base + r_in;                       // position in (permuted) query order
-        long long orow = row;
-        if (p.perm != nullptr) orow = p.perm[(size_t)it.bh * p.Sq + row];
-        epi.out = reinterpret_cast<uint8_t*>(p.out) +
-                  2 * ((size_t)it.b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)it.h * p.o_stride[2] +
-                       (size_t)x * kHalf);
-        if (x == 0 && p.lse != nullptr) epi.lse = p.lse + (size_t)it.bh * p.Sq + orow;
-      }
-      epi_has_res = p.residual != nullptr;
-      if (epi_has_res) {
-        // residual rows of this warp, coalesced, straight into the staging area
-        const uint8_t* rb = reinterpret_cast<const uint8_t*>(p.residual) +
-                            2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1] + (size_t)x * kHalf);
-        const size_t r_row = 2 * (size_t)p.r_stride[2];
-        const uint32_t st = stage_of(eic);
-        const int w_row0 = (warp & 3) * 32;
-        const int ch = lane % kCh;
-#pragma unroll
-        for (int i = 0; i < kCh; ++i) {
-          const int rl = i * kRpi + lane / kCh;                    // row inside the warp's 32 rows
-          const uint32_t dst = st + rl * kHalfBytes + ((ch ^ (rl % kCh)) << 4);
-          if (w_row0 + rl < it.rows_valid)
-            cp_async16(dst, rb + (size_t)(it.row_base + w_row0 + rl) * r_row + ch * 16);
-          else
-            cp_async16_zfill(dst, rb, 0);
-        }
-      }
-    };
-    auto epilogue_finish = [&](int eic) -> bool {
-      // eic: CTA-local index of the item being finished; its statistics were published by both streams
-      if (!mbar_wait(bar(BAR_O_FULL), eic & 1, p.status, 11)) return false;
-      if (!mbar_wait(bar(BAR_STATS), eic & 1, p.status, 14)) return false;
-      tc_fence_after();
-      // both streams' partial sums are relative to the same (shared) row maximum
-      const float m_all = stats[256 + r_in];
-      const float l_all = stats[r_in] + stats[128 + r_in];
-      const float w = epi.vscale / l_all;
-      const uint32_t tO = tmem + kColO + x * kHalf + lane_addr;
-      const uint32_t st = stage_of(eic);
-      const uint32_t my_row = st + lane * kHalfBytes;
-      cp_async_wait_all();
-      __syncwarp();
-#pragma unroll
-      for (int c = 0; c < kHalf / 16; ++c) {
-        uint32_t ra[16];
-        tmem_ld16(tO + c * 16, ra);
-        tmem_wait_ld();
-        if (c == kHalf / 16 - 1) {
-          // all of this thread's reads of O and of the statistics are done
-          tc_fence_before();
-          mbar_arrive_relaxed(bar(BAR_O_EMPTY));
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 2; ++q4) {
-          const uint32_t addr = my_row + ((((c * 2 + q4) ^ (lane % kCh))) << 4);
-          uint4 res = make_uint4(0, 0, 0, 0);
-          if (epi_has_res) res = lds_v4(addr);
-          const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
-          uint32_t ow[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 rr = unpack16<kFp16>(rw[j]);
-            const int k = q4 * 8 + 2 * j;
-            const float o0 = fmaf(__uint_as_float(ra[k]), w, rr.x);
-            const float o1 = fmaf(__uint_as_float(ra[k + 1]), w, rr.y);
-            ow[j] = pack16<kFp16>(o0, o1);
-          }
-          sts_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
-        }
-      }
-      // natural-log LSE of the scaled logits
-      if (epi.lse != nullptr) *epi.lse = (m_all + lg2_approx(l_all) - kBias) * 0.6931471805599453f;
-      __syncwarp();
-      // coalesced write-out: kCh lanes per output row
-      const unsigned long long my_out = reinterpret_cast<unsigned long long>(epi.out);
-      const int ch = lane % kCh;
-#pragma unroll
-      for (int i = 0; i < kCh; ++i) {
-        const int rl = i * kRpi + lane / kCh;
-        const unsigned long long optr = __shfl_sync(0xffffffffu, my_out, rl);
-        const uint4 v = lds_v4(st + rl * kHalfBytes + ((ch ^ (rl % kCh)) << 4));
-        if (optr != 0ull) *reinterpret_cast<uint4*>(optr + ch * 16) = v;
-      }
-      __syncwarp();
-      mbar_arrive(bar(BAR_STAGE_FREE + (eic & 1)));          // the staging area (a Q buffer) may be refilled
-      return true;
-    };
-
-    bool epi_pending = false;   // the previous item still needs its epilogue
+    constexpr int kHalf = D / 2;                 // output columns whose accumulator this stream rescales
     bool s_ready = false;       // next tile's score barrier was already complete when probed
     const int pair_bar = 1 + (warp & 3);            // named barrier of this row block's two warps (w, w+4)
     const uint32_t tOh = tmem + kColO + x * kHalf + lane_addr;   // this thread's half of its output row
@@ -430,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         tmem_ld32(tSx + 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive_relaxed(bar(BAR_S_FREE + buf));
+        warp_arrive(bar(BAR_S_FREE + buf));
         TL(8, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // P[buf] was last read by P V of tile g-2: probe now, wait (if at all) just before the stores
         const bool p_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
@@ -523,36 +422,30 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         tmem_wait_st();
         TL(20, g, x == 0 && lane == 0 && (warp & 3) == 0);
         tc_fence_before();
-        mbar_arrive_relaxed(bar(BAR_P_READY + 2 * x + buf));
+        warp_arrive(bar(BAR_P_READY + 2 * x + buf));
         TR_END(6);   // st + arrive
         TL(x == 0 ? 9 : 11, g, lane == 0 && (warp & 3) == 0);
-        if (t == 0 && epi_pending) {
-          // the previous item's last P V completed long ago: finish it now
-          ok = epilogue_finish(ic - 1);
-          epi_pending = false;
-          if (!ok) break;
-          TR_END(8);   // deferred epilogue
-        }
         if (t == it.T - 1) {
-          // Last tile done: publish this stream's (max, sum) (the previous item's were consumed by
-          // the epilogue above) and issue the residual reads of this row.
-          // (every thread of both streams must have read the previous item's statistics: normally
-          // long true, the wait only matters for items of one or two tiles)
+          // Last tile done: publish this stream's partial row sum (and the shared max) for the epilogue
+          // warps, once they have read the previous item's (normally long true).
           if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
           if (!ok) break;
           TR_END(9);   // wait previous O_EMPTY
           stats[x * 128 + r_in] = l_run;
           if (x == 0) stats[256 + r_in] = m_run;
-          mbar_arrive(bar(BAR_STATS));
+          warp_arrive(bar(BAR_STATS));
           TR_END(10);  // stats store + arrive
-          epilogue_prepare(it, ic);
-          epi_pending = true;
-          TR_END(7);   // publish stats, issue residual reads
         }
       }
       if (!ok) break;
     }
-    if (ok && epi_pending) ok = epilogue_finish(ic - 1);
+#if defined(MCS_CLK)
+    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
+      p.trace[0] = clock64() - clk_c0;
+      p.trace[1] = static_cast<long long>(globaltimer_ns() - clk_g0);
+      p.trace[2] = g;
+    }
+#endif
     TR_FLUSH(x, lane == 0 && (warp & 3) == 0);
     tc_fence_before();
   } else if (warp < kMmaWarp) {
@@ -692,6 +585,125 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     cp_async_wait_all();
     tc_fence_before();
     TR_FLUSH(2, pw == 0 && lane == 0);
+  } else if (warp >= kEpiWarp0) {
+    // =====================================================================
+    // epilogue warps: one per tensor-memory lane group, thread == query row.
+    //
+    // out = O / (l_A + l_B) + residual, rounded once to the output type and written to the row's
+    // original position.  The softmax warps are the busiest part of the CTA, so nothing of this
+    // runs there: these four warps pick a finished item up as soon as its last P V has completed,
+    // copy O out of tensor memory (after which the next item's first P V may overwrite it) and do
+    // the global traffic at leisure while the next item is already being processed.
+    //
+    // Global traffic is staged through shared memory so that every global access is coalesced: a
+    // thread owns a ROW in tensor memory, and 32 row-strided 16-byte accesses per instruction cost
+    // the load/store unit 32 wavefronts each.  Each warp has a private 32-row area, XOR-swizzled
+    // by row so that both access patterns are conflict-free.  With 16-bit inputs the area is the
+    // finished item's own Q buffer (idle once the item's last Q K^T has completed).
+    // =====================================================================
+    const int lg = warp & 3;                              // lane group of this warp
+    const int r_in = lg * 32 + lane;                      // row inside the group
+    const uint32_t lane_addr = (static_cast<uint32_t>(lg) * 32u) << 16;
+    constexpr float kBias = kFp8 ? 4.0f : 0.0f;           // P bias of the e4m3 path (see the softmax role)
+    constexpr int kRowBytes = D * 2;                      // bytes of an output row
+    constexpr int kCh = kRowBytes / 16;                   // 16-byte chunks per row
+    constexpr int kRpi = 32 / kCh;                        // rows covered by one coalesced warp access
+    auto warp_arrive = [&](uint32_t b) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b);
+    };
+    bool ok = true;
+    int ic = 0;
+#pragma unroll 1
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
+      const Item it = decode_item(p, item);
+      const int qbuf = ic & 1;
+      const uint32_t st = (kFp8 ? (s_base + L::kStage) : sQ(qbuf)) + static_cast<uint32_t>(lg) * 32u * kRowBytes;
+      const float vscale = kFp8 ? p.scale_v[it.bh] : 1.f;
+      unsigned long long my_out = 0ull;                   // this row's output address, 0 for a padding row
+      float* my_lse = nullptr;
+      if (r_in < it.rows_valid) {
+        const int row = it.row_base + r_in;               // position in (permuted) query order
+        long long orow = row;
+        if (p.perm != nullptr) orow = p.perm[(size_t)it.bh * p.Sq + row];
+        my_out = reinterpret_cast<unsigned long long>(
+            reinterpret_cast<uint8_t*>(p.out) +
+            2 * ((size_t)it.b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)it.h * p.o_stride[2]));
+        if (p.lse != nullptr) my_lse = p.lse + (size_t)it.bh * p.Sq + orow;
+      }
+      const bool has_res = p.residual != nullptr;
+      const int ch = lane % kCh;
+      // the staging area is free once the item's last Q K^T has read Q (16-bit inputs), or at once
+      if (!kFp8) ok = mbar_wait(bar(BAR_Q_EMPTY + qbuf), (ic >> 1) & 1, p.status, 40);
+      if (!ok) break;
+      if (has_res) {
+        // residual rows of this warp, coalesced, straight into the staging area
+        const uint8_t* rb = reinterpret_cast<const uint8_t*>(p.residual) +
+                            2 * ((size_t)it.b * p.r_stride[0] + (size_t)it.h * p.r_stride[1]);
+        const size_t r_row = 2 * (size_t)p.r_stride[2];
+#pragma unroll
+        for (int i = 0; i < kCh; ++i) {
+          const int rl = i * kRpi + lane / kCh;           // row inside the warp's 32 rows
+          const uint32_t dst = st + rl * kRowBytes + ((ch ^ (rl % kCh)) << 4);
+          if (lg * 32 + rl < it.rows_valid)
+            cp_async16(dst, rb + (size_t)(it.row_base + lg * 32 + rl) * r_row + ch * 16);
+          else
+            cp_async16_zfill(dst, rb, 0);
+        }
+      }
+      if (!mbar_wait(bar(BAR_O_FULL), ic & 1, p.status, 11)) { ok = false; break; }
+      if (!mbar_wait(bar(BAR_STATS), ic & 1, p.status, 14)) { ok = false; break; }
+      tc_fence_after();
+      // both streams' partial sums are relative to the same (shared) row maximum
+      const float m_all = stats[256 + r_in];
+      const float l_all = stats[r_in] + stats[128 + r_in];
+      const float w = vscale / l_all;
+      const uint32_t tO = tmem + kColO + lane_addr;
+      const uint32_t my_row = st + lane * kRowBytes;
+      cp_async_wait_all();
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) {
+        uint32_t ra[16];
+        tmem_ld16(tO + c * 16, ra);
+        tmem_wait_ld();
+        if (c == D / 16 - 1) {
+          // all of this warp's reads of O and of the statistics are done
+          tc_fence_before();
+          warp_arrive(bar(BAR_O_EMPTY));
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 2; ++q4) {
+          const uint32_t addr = my_row + ((((c * 2 + q4) ^ (lane % kCh))) << 4);
+          uint4 res = make_uint4(0, 0, 0, 0);
+          if (has_res) res = lds_v4(addr);
+          const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 rr = unpack16<kFp16>(rw[j]);
+            const int k = q4 * 8 + 2 * j;
+            const float o0 = fmaf(__uint_as_float(ra[k]), w, rr.x);
+            const float o1 = fmaf(__uint_as_float(ra[k + 1]), w, rr.y);
+            ow[j] = pack16<kFp16>(o0, o1);
+          }
+          sts_v4(addr, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+      }
+      // natural-log LSE of the scaled logits
+      if (my_lse != nullptr) *my_lse = (m_all + lg2_approx(l_all) - kBias) * 0.6931471805599453f;
+      __syncwarp();
+      // coalesced write-out: kCh lanes per output row
+#pragma unroll
+      for (int i = 0; i < kCh; ++i) {
+        const int rl = i * kRpi + lane / kCh;
+        const unsigned long long optr = __shfl_sync(0xffffffffu, my_out, rl);
+        const uint4 v = lds_v4(st + rl * kRowBytes + ((ch ^ (rl % kCh)) << 4));
+        if (optr != 0ull) *reinterpret_cast<uint4*>(optr + ch * 16) = v;
+      }
+      warp_arrive(bar(BAR_STAGE_FREE + qbuf));            // the staging area (a Q buffer) may be refilled
+    }
+    tc_fence_before();
   } else {
     // =====================================================================
     // MMA issuers: warp 12 issues every S = Q K^T, warp 13 every O += P V.  Both warps run their
