@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._pump, daemon=True)
             self.t.start()
@@ -231,10 +231,19 @@ def run_ours(args):
     for i in range(args.steps):
         step()
         ev[i + 1].record()
+    # SM clock right behind the timed region (the GPU is still under that load's power state): one CTA
+    # counting SM cycles against the nanosecond timer; nvidia-smi's poll cannot resolve a region of a
+    # few milliseconds
+    probe = torch.zeros(2, dtype=torch.int64, device=dev)
+    import ctypes
+    _lib.lib().mcs_sm_clock_probe(ctypes.c_void_p(probe.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
     per = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        pc, pn = int(probe[0]), int(probe[1])
+        clocks["sm_mhz_probe_after_timed_region"] = round(pc * 1000.0 / pn, 1) if pn > 0 else None
     _lib.check_status(dev, "bench timed region")
 
     # ---- end to end through the public entry point with host buffers

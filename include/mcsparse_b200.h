@@ -207,6 +207,15 @@ int mcs_perm_apply(const void* x, void* out, const int64_t* perm, int32_t BH, in
 int mcs_perm_invert(const void* x, void* out, const int64_t* perm, int32_t BH, int32_t L, int32_t row_bytes,
                     int64_t x_bh_bytes, int64_t x_row_bytes, int64_t o_bh_bytes, int64_t o_row_bytes, void* stream);
 
+/*
+ * SM clock probe (no reference counterpart; measurement aid).  Launches one CTA that spins for about
+ * 40,000 SM cycles and writes {SM cycles, nanoseconds} it observed to out2[0..1] (device memory, two
+ * int64): cycles * 1000 / nanoseconds is the SM clock in MHz at that moment.  Launched right behind a
+ * timed region on the same stream it reports the clock the GPU was running at under that load, which
+ * a 100 ms nvidia-smi poll cannot resolve for regions of a few milliseconds.
+ */
+int mcs_sm_clock_probe(int64_t* out2, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "mcs_pddp_perm_static",
     "mcs_perm_apply",
     "mcs_perm_invert",
+    "mcs_sm_clock_probe",
 )
 
 

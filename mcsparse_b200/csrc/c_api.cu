@@ -5,8 +5,19 @@
 #include <cmath>
 
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace {
+
+// One CTA, one thread: spins for a fixed number of SM cycles (bounded) and reports cycles and wall time.
+__global__ void sm_clock_probe_kernel(long long* out2) {
+  const long long c0 = clock64();
+  const unsigned long long g0 = mcs::globaltimer_ns();
+  long long c1 = c0;
+  for (int i = 0; i < (1 << 20) && c1 - c0 < 40000; ++i) c1 = clock64();
+  out2[0] = c1 - c0;
+  out2[1] = static_cast<long long>(mcs::globaltimer_ns() - g0);
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -18,6 +29,12 @@ extern "C" void mcs_debug_set_trace(long long* t) { g_trace = t; }
 #endif
 
 extern "C" {
+
+int mcs_sm_clock_probe(int64_t* out2, void* stream) {
+  if (out2 == nullptr) return MCS_ERR_NULL_POINTER;
+  sm_clock_probe_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<long long*>(out2));
+  return cudaGetLastError() == cudaSuccess ? 0 : MCS_ERR_LAUNCH_FAILED;
+}
 
 int mcs_version(void) { return 1; }
 int mcs_built_for_sm(void) { return 100; }

@@ -395,39 +395,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA and integer pipes instead of the special-function unit (16 results per clock per
-// SM): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, degree-3 polynomial for 2^f on
-// [-0.5, 0.5] (relative error 1.0e-4, below the rounding of a 16-bit P), exponent added with integer
-// arithmetic.  Valid for x <= 127; inputs below -126 flush towards the smallest normal numbers.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;                 // integer part in the low mantissa bits
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(0.05500889f, f, 0.24221097f);
-  p = fmaf(p, f, 0.69328294f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-// Packed pairs of fp32 values (sm_100 executes fma/add on two lanes of a 64-bit register pair
-// with one instruction) and the three-input maximum.
-__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void f32x2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
+// Three-input maximum (one instruction on sm_100).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
