@@ -188,22 +188,31 @@ def run_ours(args):
     out = torch.empty_like(q)
 
     if world > 1:
-        from mcsparse_b200.h3.context_parallel import UlyssesSparseAttention
-        ul = UlyssesSparseAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
+        from mcsparse_b200.h3.context_parallel import UlyssesFusedAttention, UlyssesSparseAttention
         Ls = L // world
         q_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
         k_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
         v_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
-        o_chunks = [torch.empty(1, L, ul.hc, D, device=dev, dtype=torch.bfloat16) for _ in range(ul.chunks)]
+        if args.ulysses == "fused":
+            # peer-store scatter in front, attention epilogue storing into the owners' sequence shards
+            ul = UlyssesFusedAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
 
-        def attn(qh, kh, vh, h0, h1):
-            o = o_chunks[h0 // ul.hc]
-            flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], out=o, residual=residual[:, h0:h1])
-            return o
+            def attn(qh, kh, vh, h0, h1, out_peers):
+                flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], residual=residual[:, h0:h1], out_peers=out_peers)
+            launches_per_step = 4 * ul.chunks            # 3 scatters + 1 attention per head chunk
+        else:
+            # library all-to-alls around the attention (comparison arm)
+            ul = UlyssesSparseAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
+            o_chunks = [torch.empty(1, L, ul.hc, D, device=dev, dtype=torch.bfloat16) for _ in range(ul.chunks)]
+
+            def attn(qh, kh, vh, h0, h1):
+                o = o_chunks[h0 // ul.hc]
+                flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], out=o, residual=residual[:, h0:h1])
+                return o
+            launches_per_step = ul.chunks
 
         def step():
             return ul.forward(q_s, k_s, v_s, attn)
-        launches_per_step = ul.chunks
     else:
         def step():
             flash_attn_gather_kv_func(q, k, v, gi, out=out, residual=residual)
@@ -297,7 +306,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": shape.n_groups,
                        "topk": shape.topk, "residual": "fused", "indices": "4 sinks + top-2044 by exact fp32 group mass, ascending",
-                       "parallelism": f"ulysses{world}" if world > 1 else "single",
+                       "parallelism": f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" if world > 1 else "single",
                        "l2": "inputs (1.06 GB per call) larger than L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
@@ -387,6 +396,8 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=3, help="head chunks of the Ulysses pipeline (N > 1)")
+    ap.add_argument("--ulysses", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: peer-store reshard fused with the attention kernel, or library all-to-alls around it")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU)")

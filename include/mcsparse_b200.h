@@ -100,6 +100,33 @@ typedef struct mcs_gather_attn_args {
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* args, void* stream);
 
 /*
+ * The same kernel with a SEQUENCE-SHARDED output: row r' of the output is written to
+ * out_peers[r' / rows_per_peer] at local row r' % rows_per_peer (strides args->o_stride, batch and head
+ * offsets as usual; args->out is ignored).  out_peers is a host array of n_peers (<= 16) device pointers
+ * that this GPU can store to: its own memory and peers' memory mapped into this process (CUDA IPC or
+ * virtual-memory handles, NVLink).  This is the head-to-sequence all-to-all of Ulysses context
+ * parallelism fused into the attention epilogue: each finished row goes straight to the rank that owns
+ * its token, so no reverse all-to-all and no unpack copy exist.
+ *
+ * Replaces: the second all-to-all of diffusers' _templated_context_parallel_attention around the
+ * reference's forward_op (mcsparse/h3/context_parallel.py:220-229).  The caller orders the launch
+ * against the peers' later reads (a stream-ordered collective or event exchange); nothing in the kernel
+ * waits for another GPU.
+ */
+int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* args, void* const* out_peers, int32_t n_peers,
+                                int32_t rows_per_peer, void* stream);
+
+/*
+ * Sequence-to-head reshard by peer stores (the first all-to-all of the same path): src holds `rows`
+ * local tokens of src_row_bytes each; the seg_bytes at offset r * seg_stride_bytes of a row are the heads
+ * wanted by rank r (all of its heads, or a chunk of them when the exchange is pipelined), and are written
+ * to dst_peers[r] + (rank * rows + s) * seg_bytes for local row s.  dst_peers is a host array of device
+ * pointers this GPU can store to (see above).  16-byte granularity.
+ */
+int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                        int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream);
+
+/*
  * Anchor-step group mass: mass[b,h,m,j] = sum_{i in group m} exp(scale * q_i . k_j - lse_i), fp32.
  *
  * Replaces: mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-117

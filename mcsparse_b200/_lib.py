@@ -16,6 +16,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libmcsparse_b200.so"
 MCS_DTYPE_BF16 = 0
 MCS_DTYPE_FP16 = 1
 MCS_DTYPE_E4M3 = 2
+# argument-error codes of include/mcsparse_b200.h
+MCS_ERR_NULL_POINTER, MCS_ERR_BAD_SHAPE, MCS_ERR_BAD_HEAD_DIM, MCS_ERR_BAD_DTYPE, MCS_ERR_BAD_ALIGNMENT = -1, -2, -3, -4, -5
 
 # Every symbol the header declares; the CPU test-suite checks this list against
 # the header and against the built library.
@@ -24,6 +26,8 @@ EXPORTED_SYMBOLS = (
     "mcs_built_for_sm",
     "mcs_error_string",
     "mcs_gather_attn_fwd",
+    "mcs_gather_attn_fwd_sharded",
+    "mcs_ulysses_scatter",
     "mcs_group_mass",
     "mcs_topk_select",
     "mcs_pddp_workspace_bytes",
@@ -99,6 +103,14 @@ def lib() -> C.CDLL:
     L.mcs_error_string.argtypes = [C.c_int]
     L.mcs_gather_attn_fwd.restype = C.c_int
     L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
+    L.mcs_gather_attn_fwd_sharded.restype = C.c_int
+    L.mcs_gather_attn_fwd_sharded.argtypes = [C.POINTER(GatherAttnArgs), C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                              C.c_void_p]
+    L.mcs_ulysses_scatter.restype = C.c_int
+    L.mcs_ulysses_scatter.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_int64,
+                                      C.c_int64, C.c_int64, C.c_void_p]
+    L.mcs_sm_clock_probe.restype = C.c_int
+    L.mcs_sm_clock_probe.argtypes = [C.c_void_p, C.c_void_p]
     L.mcs_group_mass.restype = C.c_int
     L.mcs_group_mass.argtypes = [C.POINTER(GroupMassArgs), C.c_void_p]
     L.mcs_topk_select.restype = C.c_int

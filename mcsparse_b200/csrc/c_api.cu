@@ -56,10 +56,19 @@ const char* mcs_error_string(int code) {
   }
 }
 
-int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
-  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->out == nullptr ||
-      a->gi == nullptr || a->status == nullptr)
+static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_peers, int n_peers, int rows_per_peer,
+                                void* stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->gi == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
+  if (n_peers == 0 && a->out == nullptr) return MCS_ERR_NULL_POINTER;
+  if (n_peers > 0) {
+    if (out_peers == nullptr) return MCS_ERR_NULL_POINTER;
+    if (n_peers > 16 || rows_per_peer < 1 || (long long)rows_per_peer * n_peers < a->Sq) return MCS_ERR_BAD_SHAPE;
+    for (int i = 0; i < n_peers; ++i) {
+      if (out_peers[i] == nullptr) return MCS_ERR_NULL_POINTER;
+      if (!aligned16(out_peers[i])) return MCS_ERR_BAD_ALIGNMENT;
+    }
+  }
   if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return MCS_ERR_BAD_SHAPE;
   if (a->gather_len < 128 || a->gather_len % 128 != 0) return MCS_ERR_BAD_SHAPE;
   if (a->group_rows < 1 || a->group_rows > 128) return MCS_ERR_BAD_SHAPE;
@@ -67,7 +76,7 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
     return MCS_ERR_BAD_DTYPE;
   const int esize = a->dtype == MCS_DTYPE_E4M3 ? 1 : 2;
   const int row_align = 16 / esize;  // elements per 16 bytes
-  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out) ||
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || (a->out != nullptr && !aligned16(a->out)) ||
       (a->residual != nullptr && !aligned16(a->residual)))
     return MCS_ERR_BAD_ALIGNMENT;
   for (int i = 0; i < 3; ++i) {
@@ -88,6 +97,8 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
   }
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.H = a->H; p.D = a->D;
   p.M = (int)groups; p.gather_len = a->gather_len; p.group_rows = a->group_rows;
+  p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
+  for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #if defined(MCS_TRACE) || defined(MCS_CLK)
   p.trace = g_trace;
@@ -103,6 +114,30 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
   if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   return mcs::launch_gather_attn_16bit(p, a->dtype == MCS_DTYPE_FP16, s);
+}
+
+int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
+  return gather_attn_dispatch(a, nullptr, 0, 0, stream);
+}
+
+int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* a, void* const* out_peers, int32_t n_peers,
+                                int32_t rows_per_peer, void* stream) {
+  if (n_peers < 1) return MCS_ERR_BAD_SHAPE;
+  return gather_attn_dispatch(a, out_peers, n_peers, rows_per_peer, stream);
+}
+
+int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                        int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream) {
+  if (src == nullptr || dst_peers == nullptr) return MCS_ERR_NULL_POINTER;
+  if (n_peers < 1 || n_peers > 16 || rank < 0 || rank >= n_peers || rows < 0 || seg_bytes < 16) return MCS_ERR_BAD_SHAPE;
+  if (seg_stride_bytes < seg_bytes || src_row_bytes < seg_stride_bytes * (n_peers - 1) + seg_bytes) return MCS_ERR_BAD_SHAPE;
+  if (seg_bytes % 16 || seg_stride_bytes % 16 || src_row_bytes % 16 || !aligned16(src)) return MCS_ERR_BAD_ALIGNMENT;
+  for (int i = 0; i < n_peers; ++i) {
+    if (dst_peers[i] == nullptr) return MCS_ERR_NULL_POINTER;
+    if (!aligned16(dst_peers[i])) return MCS_ERR_BAD_ALIGNMENT;
+  }
+  return mcs::launch_ulysses_scatter(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes,
+                                     static_cast<cudaStream_t>(stream));
 }
 
 int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {

@@ -626,9 +626,17 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         const int row = it.row_base + r_in;               // position in (permuted) query order
         long long orow = row;
         if (p.perm != nullptr) orow = p.perm[(size_t)it.bh * p.Sq + row];
+        uint8_t* obase = reinterpret_cast<uint8_t*>(p.out);
+        long long lrow = orow;
+        if (p.n_out_peers > 0) {
+          // sequence-sharded output: the row belongs to rank orow / rows_per_peer; the store below goes
+          // straight into that rank's memory (the all-to-all back of Ulysses, fused into this epilogue)
+          const int peer = static_cast<int>(orow / p.out_rows_per_peer);
+          lrow = orow - (long long)peer * p.out_rows_per_peer;
+          obase = reinterpret_cast<uint8_t*>(p.out_peer[peer]);
+        }
         my_out = reinterpret_cast<unsigned long long>(
-            reinterpret_cast<uint8_t*>(p.out) +
-            2 * ((size_t)it.b * p.o_stride[0] + (size_t)orow * p.o_stride[1] + (size_t)it.h * p.o_stride[2]));
+            obase + 2 * ((size_t)it.b * p.o_stride[0] + (size_t)lrow * p.o_stride[1] + (size_t)it.h * p.o_stride[2]));
         if (p.lse != nullptr) my_lse = p.lse + (size_t)it.bh * p.Sq + orow;
       }
       const bool has_res = p.residual != nullptr;

@@ -22,6 +22,11 @@ struct GatherAttnParams {
   int B, Sq, Sk, H, D, M, gather_len, group_rows;
   float scale_log2;  // softmax_scale * log2(e)
   long long* trace;  // diagnostics builds only (MCS_TRACE): per-role event clocks of CTA 0
+  // sequence-sharded output (Ulysses): row r' of the output goes to out_peer[r' / out_rows_per_peer] at local
+  // row r' % out_rows_per_peer (peer or local memory alike)
+  void* out_peer[16];
+  int n_out_peers;          // 0 = not sharded
+  int out_rows_per_peer;
 };
 
 struct GroupMassParams {
@@ -79,5 +84,9 @@ int launch_topk_select(const TopkParams& p, cudaStream_t stream);
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
+
+// Sequence-to-head reshard by peer stores (see reshard.cu)
+int launch_ulysses_scatter(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
+                           long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);
 
 }  // namespace mcs

@@ -202,3 +202,140 @@ class UlyssesSparseAttention:
         for o in outs:
             o.record_stream(self.s_bwd)
         return self._out
+
+
+def ulysses_scatter(src: torch.Tensor, dst_ptrs: Sequence[int], rank: int, rows: int, seg_bytes: int,
+                    seg_stride_bytes: int, src_row_bytes: int) -> None:
+    """Launch ``mcs_ulysses_scatter`` on the current stream: segment r of every local row goes to peer r."""
+    import ctypes as C
+    from .. import _lib
+    table = (C.c_void_p * len(dst_ptrs))(*[int(x) for x in dst_ptrs])
+    stream = torch.cuda.current_stream(src.device).cuda_stream
+    rc = _lib.lib().mcs_ulysses_scatter(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows),
+                                        int(seg_bytes), int(seg_stride_bytes), int(src_row_bytes), C.c_void_p(stream))
+    if rc != 0:
+        raise RuntimeError(f"mcs_ulysses_scatter: {_lib.error_string(rc)} (code {rc})")
+
+
+class PeerBuffers:
+    """Peer-mapped buffers of the fused Ulysses path for one rank.
+
+    ``recv[c]`` is this rank's (3, L, hc, D) buffer for head chunk c (q, k, v of hc local heads, all tokens),
+    ``out`` its (Ls, H, D) sequence shard of the output; ``recv_ptrs[c][r]`` / ``out_ptrs[r]`` are the
+    addresses under which THIS process can store into rank r's copies.  In a real job they come from
+    ``torch.distributed._symmetric_memory`` (:meth:`symmetric`); a single process can emulate all ranks on
+    one GPU with plain tensors (:meth:`emulated`), which is how the kernels are tested without N GPUs.
+    """
+
+    def __init__(self, recv, out, recv_ptrs, out_ptrs, keep=None):
+        self.recv, self.out, self.recv_ptrs, self.out_ptrs, self._keep = recv, out, recv_ptrs, out_ptrs, keep
+
+    @staticmethod
+    def symmetric(group, world, L, Ls, H, hc, chunks, D, dtype, device) -> "PeerBuffers":
+        import torch.distributed._symmetric_memory as symm_mem
+        recv, recv_ptrs, keep = [], [], []
+        for _ in range(chunks):
+            t = symm_mem.empty((3, L, hc, D), dtype=dtype, device=device)
+            h = symm_mem.rendezvous(t, group)
+            recv.append(t)
+            recv_ptrs.append([int(h.buffer_ptrs[r]) for r in range(world)])
+            keep.append(h)
+        out = symm_mem.empty((Ls, H, D), dtype=dtype, device=device)
+        ho = symm_mem.rendezvous(out, group)
+        keep.append(ho)
+        return PeerBuffers(recv, out, recv_ptrs, [int(ho.buffer_ptrs[r]) for r in range(world)], keep)
+
+    @staticmethod
+    def emulated(world, L, Ls, H, hc, chunks, D, dtype, device) -> list:
+        """Buffers of all ``world`` ranks in this process (one GPU)."""
+        recv = [[torch.empty(3, L, hc, D, dtype=dtype, device=device) for _ in range(chunks)] for _ in range(world)]
+        out = [torch.empty(Ls, H, D, dtype=dtype, device=device) for _ in range(world)]
+        recv_ptrs = [[recv[r][c].data_ptr() for r in range(world)] for c in range(chunks)]
+        out_ptrs = [out[r].data_ptr() for r in range(world)]
+        return [PeerBuffers(recv[r], out[r], recv_ptrs, out_ptrs) for r in range(world)]
+
+
+class UlyssesFusedAttention:
+    """Ulysses attention core on peer memory, for batch size 1.
+
+    Forward reshard: one ``mcs_ulysses_scatter`` launch per tensor pushes the head slices of the local
+    sequence shard into the peers' (L, heads, D) buffers with NVLink stores (no pack copy, no library
+    all-to-all).  Backward reshard: none as a separate step - the attention kernel's epilogue stores every
+    finished row straight into the sequence shard of the rank that owns its token
+    (``mcs_gather_attn_fwd_sharded``).  The local heads are processed in chunks so that the scatter of
+    chunk c+1 (communication stream) runs under the attention of chunk c.  Kernels of different ranks are
+    ordered by two stream-ordered one-element all-reduces per step (one per chunk in front of the
+    attention, one behind the last attention); no kernel ever waits for another GPU.
+
+    ``attn_fn(q, k, v, h0, h1, out_peers)`` gets (1, L, hc, D) tensors of local heads [h0, h1) and must call
+    the attention with ``out_peers=out_peers``.  Replaces diffusers'
+    ``_templated_context_parallel_attention`` around the reference's forward_op
+    (mcsparse/h3/context_parallel.py:220-229).
+    """
+
+    def __init__(self, group, seq_len: int, heads: int, head_dim: int, dtype, device, chunks: int = 2,
+                 buffers: Optional[PeerBuffers] = None, rank: Optional[int] = None, world: Optional[int] = None):
+        self.group = group
+        self.world = world if world is not None else dist.get_world_size(group)
+        self.rank = rank if rank is not None else dist.get_rank(group)
+        if heads % self.world or seq_len % self.world:
+            raise ValueError(f"Ulysses needs heads ({heads}) and sequence ({seq_len}) divisible by the ranks ({self.world})")
+        self.L, self.H, self.D = seq_len, heads, head_dim
+        self.Ls, self.Hl = seq_len // self.world, heads // self.world
+        self.chunks = max(1, min(chunks, self.Hl))
+        while self.Hl % self.chunks:
+            self.chunks -= 1
+        self.hc = self.Hl // self.chunks
+        self.esize = torch.empty(0, dtype=dtype).element_size()
+        if (self.hc * head_dim * self.esize) % 16:
+            raise ValueError("a head chunk of one token must be a multiple of 16 bytes")
+        self.emulated = buffers is not None
+        self.buf = buffers if buffers is not None else PeerBuffers.symmetric(
+            group, self.world, self.L, self.Ls, self.H, self.hc, self.chunks, self.D, dtype, device)
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.flag_back = torch.zeros(1, dtype=torch.float32, device=device)
+        self.group_back = None
+        if not self.emulated and self.world > 1:
+            self.group_back = dist.new_group(ranks=list(range(self.world)))
+        self.s_comm = torch.cuda.Stream(device)
+
+    def _order(self, flag, group):
+        """Orders the kernels enqueued so far on every rank before what follows on this stream."""
+        if not self.emulated and self.world > 1:
+            dist.all_reduce(flag, group=group)
+
+    def scatter_chunk(self, q, k, v, c: int) -> None:
+        """Pushes head chunk c of this rank's q, k, v shards to all peers (current stream)."""
+        D, hc, Hl, H, es = self.D, self.hc, self.Hl, self.H, self.esize
+        seg, seg_stride, row = hc * D * es, Hl * D * es, H * D * es
+        plane = self.L * hc * D * es                       # bytes of one of q / k / v inside recv[c]
+        for i, t in enumerate((q, k, v)):
+            src = t.view(self.Ls, H, D)[:, c * hc:, :]     # chunk c of rank 0's heads; peers follow at seg_stride
+            ulysses_scatter(src, [p + i * plane for p in self.buf.recv_ptrs[c]], self.rank, self.Ls, seg, seg_stride, row)
+
+    def out_peers(self, c: int):
+        """(pointers, rows per peer, strides) for the attention of head chunk c."""
+        off = (self.rank * self.Hl + c * self.hc) * self.D * self.esize
+        return ([p + off for p in self.buf.out_ptrs], self.Ls, (self.Ls * self.H * self.D, self.H * self.D, self.D))
+
+    def forward(self, q, k, v, attn_fn):
+        """q, k, v: (1, L/N, H, D) sequence shards.  Returns this rank's (1, L/N, H, D) output shard."""
+        for t in (q, k, v):
+            if tuple(t.shape) != (1, self.Ls, self.H, self.D) or not t.is_contiguous():
+                raise ValueError(f"expected a contiguous sequence shard of shape {(1, self.Ls, self.H, self.D)}")
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        ev = [torch.cuda.Event() for _ in range(self.chunks)]
+        with torch.cuda.stream(self.s_comm):
+            self.s_comm.wait_event(ready)
+            for c in range(self.chunks):
+                self.scatter_chunk(q, k, v, c)
+                self._order(self.flag, self.group)
+                ev[c].record(self.s_comm)
+        for c in range(self.chunks):
+            main.wait_event(ev[c])
+            r = self.buf.recv[c]
+            attn_fn(r[0].unsqueeze(0), r[1].unsqueeze(0), r[2].unsqueeze(0), c * self.hc, (c + 1) * self.hc, self.out_peers(c))
+        self._order(self.flag_back, self.group_back)
+        return self.buf.out.unsqueeze(0)

@@ -148,9 +148,15 @@ def _extras_checks(residual, perm, q, out_dtype, batch_size, num_head, seqlen_q,
     return residual, perm
 
 
-def _launch(args: "_lib.GatherAttnArgs", device, where: str) -> None:
+def _launch(args: "_lib.GatherAttnArgs", device, where: str, out_peers=None) -> None:
     stream = torch.cuda.current_stream(device).cuda_stream
-    rc = _lib.lib().mcs_gather_attn_fwd(args, stream)
+    if out_peers is None:
+        rc = _lib.lib().mcs_gather_attn_fwd(args, stream)
+    else:
+        import ctypes as C
+        ptrs, rows_per_peer, _ = out_peers
+        table = (C.c_void_p * len(ptrs))(*[int(x) for x in ptrs])
+        rc = _lib.lib().mcs_gather_attn_fwd_sharded(args, table, len(ptrs), int(rows_per_peer), stream)
     if rc != 0:
         raise RuntimeError(f"{where}: {_lib.error_string(rc)} (code {rc})")
     if _lib.check_enabled():
@@ -192,6 +198,7 @@ def flash_attn_gather_kv_func(
     residual: Optional[torch.Tensor] = None,
     perm: Optional[torch.Tensor] = None,
     group_rows: int = 128,
+    out_peers=None,
 ):
     """Forward-only token-level sparse gather-KV attention on B200.
 
@@ -239,7 +246,15 @@ def flash_attn_gather_kv_func(
 
     device = q.device
     out_shape = (batch_size, seqlen_q, num_head, head_dim_v)
-    if out is None:
+    if out_peers is not None:
+        # sequence-sharded output (Ulysses): (pointers, rows_per_peer, (batch, row, head) element strides);
+        # every finished row is stored straight into the shard of the rank that owns its token
+        if out is not None:
+            raise ValueError("give either out or out_peers")
+        ptrs, rows_per_peer, o_strides = out_peers
+        if len(ptrs) * int(rows_per_peer) < seqlen_q:
+            raise ValueError("out_peers does not cover the query sequence")
+    elif out is None:
         out = torch.empty(out_shape, dtype=q.dtype, device=device)
     else:
         _validate_tensor(out, "out", out_shape, q.dtype, device)
@@ -253,9 +268,13 @@ def flash_attn_gather_kv_func(
     residual, perm = _extras_checks(residual, perm, q, q.dtype, batch_size, num_head, seqlen_q, head_dim_v)
 
     dtype_code = _lib.MCS_DTYPE_BF16 if q.dtype == torch.bfloat16 else _lib.MCS_DTYPE_FP16
-    args = _fill_args(q.detach(), k.detach(), v.detach(), out.detach(), lse, gather_kv_indices, gather_kv_lengths,
-                      residual, perm, gather_len, int(group_rows), dtype_code, softmax_scale)
-    _launch(args, device, "flash_attn_gather_kv_func")
+    args = _fill_args(q.detach(), k.detach(), v.detach(), q.detach() if out is None else out.detach(), lse,
+                      gather_kv_indices, gather_kv_lengths, residual, perm, gather_len, int(group_rows), dtype_code,
+                      softmax_scale)
+    if out_peers is not None:
+        args.out = None
+        args.o_stride[0], args.o_stride[1], args.o_stride[2] = (int(x) for x in out_peers[2])
+    _launch(args, device, "flash_attn_gather_kv_func", out_peers)
     return (out, lse) if return_lse else (out, None)
 
 
