@@ -211,8 +211,14 @@ def run_ours(args):
                 return o
             launches_per_step = ul.chunks
 
-        def step():
-            return ul.forward(q_s, k_s, v_s, attn)
+        if args.ulysses == "fused" and args.graph:
+            graph, _ = ul.capture(q_s, k_s, v_s, attn)
+
+            def step():
+                graph.replay()
+        else:
+            def step():
+                return ul.forward(q_s, k_s, v_s, attn)
     else:
         def step():
             flash_attn_gather_kv_func(q, k, v, gi, out=out, residual=residual)
@@ -306,7 +312,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": shape.n_groups,
                        "topk": shape.topk, "residual": "fused", "indices": "4 sinks + top-2044 by exact fp32 group mass, ascending",
-                       "parallelism": f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" if world > 1 else "single",
+                       "parallelism": (f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" + ("-graph" if args.graph and args.ulysses == "fused" else "")) if world > 1 else "single",
                        "l2": "inputs (1.06 GB per call) larger than L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
@@ -321,7 +327,15 @@ def run_ours(args):
                                     "sample": f"{heads_done} of {H} heads, all 256 groups each, {secs:.1f} s, torch fp32"}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without running destructors: symmetric-memory handles, a captured graph that contains
+        # collectives and the communicators have no defined teardown order between them, and a rank that
+        # blocks in one of them keeps the launcher (and the box) waiting after the result is out.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def run_anchor(args):
@@ -396,6 +410,7 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=3, help="head chunks of the Ulysses pipeline (N > 1)")
+    ap.add_argument("--graph", action="store_true", help="N > 1, fused: replay one captured CUDA graph per step instead of launching eagerly")
     ap.add_argument("--ulysses", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store reshard fused with the attention kernel, or library all-to-alls around it")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")

@@ -339,3 +339,17 @@ class UlyssesFusedAttention:
             attn_fn(r[0].unsqueeze(0), r[1].unsqueeze(0), r[2].unsqueeze(0), c * self.hc, (c + 1) * self.hc, self.out_peers(c))
         self._order(self.flag_back, self.group_back)
         return self.buf.out.unsqueeze(0)
+
+    def capture(self, q, k, v, attn_fn):
+        """Captures one forward (both streams, the ordering collectives included) into a CUDA graph.
+
+        A forward is a dozen short launches on two streams; replaying them as one graph takes the host out of
+        the step, which is what lets the scatter of one head chunk actually run under the attention of the
+        previous one.  Returns (graph, output shard); ``graph.replay()`` recomputes the output from the
+        current contents of q, k, v (same tensors)."""
+        self.forward(q, k, v, attn_fn)          # eager once: communicators and lazy initialisation
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward(q, k, v, attn_fn)
+        return graph, out
