@@ -401,6 +401,55 @@ def run_anchor(args):
                       "peak_source": peaks["source"]}))
 
 
+def run_fp8(args):
+    """Secondary measurement: the FP8 (e4m3) variant of the attention kernel at the long-video shape
+    (H=40, L=98,280, top-k 4096), device-resident inputs, CUDA events; random ascending indices with sinks."""
+    import math
+    import torch
+    from mcsparse_b200 import _lib, synth
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_fp8_func
+    os.environ["MCSPARSE_B200_CHECK"] = "0"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = synth.C3
+    if args.heads:
+        import dataclasses
+        shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
+    H, L, D = shape.heads, shape.seq_len, shape.head_dim
+    g = torch.Generator(device=dev).manual_seed(7)
+    mk = lambda: torch.randn(1, L, H, D, device=dev, generator=g, dtype=torch.bfloat16)
+    q8, sq = synth.quantize_e4m3_per_head(mk())
+    k8, sk = synth.quantize_e4m3_per_head(mk())
+    v8, sv = synth.quantize_e4m3_per_head(mk())
+    M = shape.n_groups
+    scale_qk = (sq * sk * (D ** -0.5) * math.log2(math.e)).view(1, H, 1).expand(1, H, M).contiguous().float()
+    # (random_sorted_indices draws per head to bound its temporary: 768 groups x 98,280 scores each)
+    residual = (0.05 * torch.randn(1, H, L, D, device=dev, generator=g)).to(torch.bfloat16)
+    gi = torch.cat([synth.random_sorted_indices(1, 1, M, shape.topk, L, seed=h, device=dev) for h in range(H)], dim=1)
+    out = torch.empty(1, L, H, D, device=dev, dtype=torch.bfloat16)
+    step = lambda: flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, scale_qk, sv.float(), out=out, residual=residual)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    _lib.check_status(dev, "fp8 warm-up")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check_status(dev, "fp8 timed region")
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * L * shape.topk * D * H
+    print(json.dumps({
+        "metric": "gather_kv_sparse_attn_fp8_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "e4m3", "data": "synthetic",
+        "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": M, "topk": shape.topk,
+                   "residual": "fused", "indices": "4 sinks + uniform sample, ascending"},
+        "gpu_launches": args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -414,13 +463,16 @@ def main():
     ap.add_argument("--ulysses", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store reshard fused with the attention kernel, or library all-to-alls around it")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
-    ap.add_argument("--workload", default="attn", choices=["attn", "anchor"],
-                    help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU)")
+    ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],
+                    help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
+                         "attn_fp8: the e4m3 variant at the long-video shape (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "anchor":
         run_anchor(args)
+    elif args.workload == "attn_fp8":
+        run_fp8(args)
     else:
         run_ours(args)
 

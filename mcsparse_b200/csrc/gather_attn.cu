@@ -306,6 +306,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     constexpr int kHalf = D / 2;                 // output columns whose accumulator this stream rescales
     bool s_ready = false;       // next tile's score barrier was already complete when probed
     const int pair_bar = 1 + (warp & 3);            // named barrier of this row block's two warps (w, w+4)
+    // where a bounded wait expired (failure path only): item, tile, and whether that tile's pair barrier was passed
+    int fail_item = 0, fail_t = 0;
+    bool fail_bar_done = false;
     const uint32_t tOh = tmem + kColO + x * kHalf + lane_addr;   // this thread's half of its output row
 #pragma unroll 1
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++ic) {
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         const int buf = g & 1;
         TR_END(0);
         if (!s_ready) ok = mbar_wait(bar(BAR_S_FULL + buf), (g >> 1) & 1, p.status, 10);
-        if (!ok) break;
+        if (!ok) { fail_item = item; fail_t = t; fail_bar_done = false; break; }
         tc_fence_after();
         TR_END(1);   // wait S_FULL
         TL(x == 0 ? 7 : 10, g, lane == 0 && (warp & 3) == 0);
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           l_run *= alpha;
           if (t > 0) {
             ok = mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, p.status, 12);
-            if (!ok) break;
+            if (!ok) { fail_item = item; fail_t = t; fail_bar_done = true; break; }
             tc_fence_after();
 #pragma unroll 1
             for (int c = 0; c < kHalf / 8; ++c) {
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         const float neg_m = kBias - m_run;
         TL(17, g, x == 0 && lane == 0 && (warp & 3) == 0);
         if (!p_free) ok = mbar_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1, p.status, 15);
-        if (!ok) break;
+        if (!ok) { fail_item = item; fail_t = t; fail_bar_done = true; break; }
         TL(18, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // exp2, partial row sum, pack, store P: 16 values (8 or 4 columns) at a time
         const uint32_t tPx = tmem + kColP + buf * 64 + x * 32 + lane_addr;
@@ -429,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           // Last tile done: publish this stream's partial row sum (and the shared max) for the epilogue
           // warps, once they have read the previous item's (normally long true).
           if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
-          if (!ok) break;
+          if (!ok) { fail_item = item; fail_t = t; fail_bar_done = true; break; }
           TR_END(9);   // wait previous O_EMPTY
           stats[x * 128 + r_in] = l_run;
           if (x == 0) stats[256 + r_in] = m_run;
@@ -438,6 +441,23 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         }
       }
       if (!ok) break;
+    }
+    if (!ok) {
+      // Failure path: a bounded wait expired (the status word says where).  The partner warp of this row
+      // block may still be running; a named barrier has no bounded wait, so this warp keeps meeting the
+      // partner at the pair barrier once per remaining tile (and at the exchange barrier whenever the
+      // OR says so), until the partner runs into its own expired wait and ends the same way.
+      int item = fail_item, t = fail_t;
+      bool done = fail_bar_done;
+      while (item < n_items) {
+        const int T = decode_item(p, item).T;
+        for (; t < T; ++t) {
+          if (!done && named_bar_red_or(pair_bar, 64, false)) named_bar_sync(pair_bar, 64);
+          done = false;
+        }
+        t = 0;
+        item += gridDim.x;
+      }
     }
 #if defined(MCS_CLK)
     if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {

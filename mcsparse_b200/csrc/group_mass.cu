@@ -21,8 +21,11 @@
 // q_i . k_j - lse_i / scale and each element costs one multiply, one ex2 and one add.
 // The kernel is bound by the ex2 throughput of the SFU (16 per clock per SM).
 //
-// Roles: warps 0-3 exponentiate and sum (thread = key token), warp 4 issues the MMAs,
-// warps 5-8 stream the key tiles with cp.async into a 3-slot ring.
+// Roles: warps 0-7 exponentiate and sum (two threads per key token: warps w and w+4 share a TMEM
+// lane group and take 64 query columns each, so that every SM sub-partition has two warps feeding
+// its SFU; the two partial sums meet in shared memory), warp 8 issues the MMAs (converged, one
+// elected lane executes the tcgen05 instructions), warps 9-12 stream the key tiles with cp.async
+// into a 3-slot ring.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -34,15 +37,17 @@ namespace mcs {
 namespace {
 
 constexpr int kTile = 128;
-constexpr int kThreads = 288;
-constexpr int kExpThreads = 128;
+constexpr int kThreads = 416;
+constexpr int kExpWarps = 8;
 constexpr int kProducerThreads = 128;
-constexpr int kMmaWarp = 4;
+constexpr int kMmaWarp = 8;
+constexpr int kProducerWarp0 = 9;
 constexpr int kRing = 3;
 constexpr uint32_t kTmemCols = 256;   // two score buffers of 128 columns
 
 enum { BAR_FULL = 0, BAR_EMPTY = BAR_FULL + kRing, BAR_Q_FULL = BAR_EMPTY + kRing, BAR_S_FULL, BAR_S_FREE = BAR_S_FULL + 2,
-       BAR_DRAIN = BAR_S_FREE + 2, BAR_COUNT };
+       BAR_PART = BAR_S_FREE + 2,      // [4 lane groups][2 bufs]: partial sums of the upper column half are in shared memory
+       BAR_DRAIN = BAR_PART + 8, BAR_COUNT };
 
 template <int D>
 struct Smem {
@@ -53,7 +58,8 @@ struct Smem {
   static constexpr int kKx = kQx + 16384;                   // extra k-step of K: constant (1,1,1,0...)
   static constexpr int kRingOff = kKx + 16384;
   static constexpr int kBars = kRingOff + kRing * kTileBytes;
-  static constexpr int kTmemSlot = kBars + BAR_COUNT * 8;
+  static constexpr int kPart = kBars + BAR_COUNT * 8;       // float [2][128]: partial sums of the upper column half
+  static constexpr int kTmemSlot = kPart + 2 * 128 * 4;
   static constexpr int kTotal = kTmemSlot + 16;
   static constexpr int kDynamic = kTotal + 1024;
 };
@@ -72,7 +78,8 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
   auto bar = [&](int i) { return bars + 8u * i; };
   auto sRing = [&](int slot) { return s_base + L::kRingOff + slot * L::kTileBytes; };
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // provably warp-uniform
 
   const int m = blockIdx.x % p.M;
   const int bh = blockIdx.x / p.M;
@@ -89,8 +96,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
     mbar_init(bar(BAR_Q_FULL), 2 * kProducerThreads);   // per thread: its cp.async rows + its plain stores
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(BAR_S_FULL + i), 1);
-      mbar_init(bar(BAR_S_FREE + i), kExpThreads);
+      mbar_init(bar(BAR_S_FREE + i), kExpWarps);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(bar(BAR_PART + i), 1);
     mbar_init(bar(BAR_DRAIN), 1);
     mbar_fence_init();
   }
@@ -103,13 +111,15 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < kExpWarps) {
     // ===================================================================== exp + column sum
-    const int j_in = warp * 32 + lane;                 // key token inside the tile == TMEM lane
-    const uint32_t lane_addr = (static_cast<uint32_t>(warp) * 32u) << 16;
+    const int lg = warp & 3, x = warp >> 2;            // TMEM lane group, column half
+    const int j_in = lg * 32 + lane;                   // key token inside the tile == TMEM lane
+    const uint32_t lane_addr = (static_cast<uint32_t>(lg) * 32u) << 16;
     const float c = p.scale_log2;
     const float norm = p.normalize ? 1.f / static_cast<float>(rows_valid) : 1.f;
     float* out = p.mass + ((size_t)bh * p.M + m) * p.Lk;
+    float* part = reinterpret_cast<float*>(smem + L::kPart);
     bool ok = true;
 #pragma unroll 1
     for (int t = 0; t < n_tiles && ok; ++t) {
@@ -119,9 +129,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
       tc_fence_after();
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < 2; ++q) {
         uint32_t r[32];
-        tmem_ld32(tmem + buf * 128 + q * 32 + lane_addr, r);
+        tmem_ld32(tmem + buf * 128 + x * 64 + q * 32 + lane_addr, r);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -132,14 +142,33 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
         }
       }
       tc_fence_before();
-      mbar_arrive_relaxed(bar(BAR_S_FREE + buf));
-      const int j = t * kTile + j_in;
-      if (j < p.Lk) out[j] = ((a0 + a1) + (a2 + a3)) * norm;
+      const float sum = (a0 + a1) + (a2 + a3);
+      // The two halves of a row meet in shared memory, double-buffered by tile parity and handed over
+      // through an mbarrier (a bounded wait, unlike a named barrier).  The lower half releases the score
+      // buffer only after it has read the partner's sums, so the partner's write two tiles later (which
+      // needs that release to get its next scores) cannot overtake the read.  (Copying all 64 values to
+      // registers first and releasing the score buffer before the exponentials measured 10% slower.)
+      if (x == 1) {
+        part[buf * 128 + j_in] = sum;
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(BAR_PART + 2 * lg + buf));
+          mbar_arrive(bar(BAR_S_FREE + buf));              // one arrival per warp
+        }
+      } else {
+        ok = mbar_wait(bar(BAR_PART + 2 * lg + buf), (t >> 1) & 1, p.status, 45);
+        if (!ok) break;
+        const int j = t * kTile + j_in;
+        if (j < p.Lk) out[j] = (sum + part[buf * 128 + j_in]) * norm;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_S_FREE + buf));
+      }
     }
     tc_fence_before();
   } else if (warp == kMmaWarp) {
     // ===================================================================== MMA issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       constexpr uint32_t kFmt = kFp16 ? 0u : 1u;
       constexpr uint32_t idesc = mma_idesc(kFmt, kFmt, 0, 0, 128, 128);
       constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -163,15 +192,17 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
           const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
-          mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);     // A = K tile, B = Q group
+          if (leader) mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);     // A = K tile, B = Q group
         }
-        mma_f16_ss(tS, desc(kxlo), desc(qxlo), idesc, 1);                       // extra k-step: - lse / scale
-        tc_commit(bar(BAR_EMPTY + slot));
-        tc_commit(bar(BAR_S_FULL + buf));
+        if (leader) {
+          mma_f16_ss(tS, desc(kxlo), desc(qxlo), idesc, 1);                     // extra k-step: - lse / scale
+          tc_commit(bar(BAR_EMPTY + slot));
+          tc_commit(bar(BAR_S_FULL + buf));
+        }
         if (++slot == kRing) { slot = 0; phase ^= 1; }
       }
       if (!ok) {
-        tc_commit(bar(BAR_DRAIN));
+        if (leader) tc_commit(bar(BAR_DRAIN));
         mbar_wait_quiet(bar(BAR_DRAIN), 0, 1 << 20);
       }
     }
@@ -179,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
     tc_fence_before();
   } else {
     // ===================================================================== producers
-    const int pw = warp - 5;
+    const int pw = warp - kProducerWarp0;
     const int ptid = pw * 32 + lane;                    // 0..127: also the row this thread prepares
     const int row0 = pw * 32;
     constexpr int kChunks = D / 8;

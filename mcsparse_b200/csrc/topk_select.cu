@@ -11,7 +11,7 @@
 // here the dropped entries are the lowest-ranked ones and the output is sorted.
 //
 // Algorithm per row (1024 threads):
-//   1. map scores to order-preserving 32-bit keys (NaN lowest; sinks get key 0, below every real
+//   1. map scores to order-preserving 32-bit keys (NaN highest; sinks get key 0, below every real
 //      key) and stage the row in shared memory when it fits (<= ~200 KB), else re-read it from L2;
 //   2. MSB-first radix select, four 8-bit passes with warp-aggregated shared-memory histograms,
 //      finds the key T of the k-th largest element and how many elements equal to T are needed;
@@ -33,10 +33,10 @@ constexpr int kMaxSinks = 64;
 
 __device__ __forceinline__ uint32_t score_key(float s) {
   uint32_t u = __float_as_uint(s);
-  if (s != s) return 1u;                                  // NaN: below every number
+  if (s != s) return 0xFFFFFFFFu;                         // NaN: above every number, as torch.topk ranks it
   if (s == 0.f) u = 0u;                                   // -0 and +0 rank equal
   u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);          // order-preserving
-  return u < 2u ? 2u : u;                                  // keep 0 (sink) and 1 (NaN) reserved
+  return u < 2u ? 2u : u;                                  // keep 0 (sink) and 1 (padding) reserved
 }
 
 struct Shared {

@@ -51,3 +51,30 @@ def test_reference_shaped_wrapper(cuda_device):
     gi2, gl2 = _select_topk_tokens(tp.to(cuda_device), 0.25)
     assert tuple(gi2.shape) == (1, 2, 3, 256) and gl2 is None
     assert torch.equal(gi2.cpu(), select_topk_ref(tp, 256))
+
+
+@pytest.mark.parametrize("L", [32768, 32761, 4100])
+def test_register_path_structured_rows(cuda_device, L):
+    """Rows that defeat the sampled lower bound of the register-resident kernel (it must only cost time):
+    ramps, the winners hidden between the sampled positions, NaN-heavy and constant rows, a few NaNs."""
+    g = torch.Generator().manual_seed(L)
+    k_total = 2048 if L > 5000 else 512
+    rows = []
+    rows.append(torch.arange(L).float())                                   # winners at the end
+    rows.append(torch.arange(L, 0, -1).float())                            # winners at the start
+    hidden = torch.zeros(L)
+    pos = torch.arange(1, L, 4)[: k_total + 100]                           # never a sampled position (those are multiples of 4)
+    hidden[pos] = 1.0 + torch.rand(pos.numel(), generator=g)
+    rows.append(hidden)
+    nan_row = torch.rand(L, generator=g)
+    nan_row[torch.randperm(L, generator=g)[: L - 500]] = float("nan")      # NaN ranks highest (torch.topk): a huge tie at the top
+    rows.append(nan_row)
+    rows.append(torch.full((L,), 0.25))                                    # constant row
+    rows.append(torch.rand(L, generator=g) ** 16)                          # mass-like
+    few = torch.rand(L, generator=g)
+    few[torch.randperm(L, generator=g)[:37]] = float("nan")
+    rows.append(few)
+    scores = torch.stack(rows)
+    out = _run(cuda_device, scores, k_total, [(0, 4)])
+    ref = select_topk_ref(scores, k_total, sinks=range(4))
+    assert torch.equal(out, ref)
