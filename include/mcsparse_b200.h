@@ -100,6 +100,18 @@ typedef struct mcs_gather_attn_args {
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* args, void* stream);
 
 /*
+ * Dense attention with log-sum-exp through the same kernel: every query group attends to all Sk keys
+ * (args->gi, gl, gather_len are ignored; bf16 / fp16 only; the part of the last 128-key tile beyond Sk is
+ * masked).  residual, perm and lse work as above.  This is the input of the anchor step: the dense output
+ * (returned on anchor steps, and the minuend of the cached residual) and the per-row LSE that
+ * mcs_group_mass needs.
+ *
+ * Replaces: the FlashAttention-3 call of mcsparse/kernels/flash_mcsa/ops/full_attn.py:88-121 as used by
+ * mcsparse/kernels/flash_mcsa/token_sparse.py:1151 (dense pass with LSE in the calibrate branch).
+ */
+int mcs_dense_attn_fwd(const mcs_gather_attn_args* args, void* stream);
+
+/*
  * The same kernel with a SEQUENCE-SHARDED output: row r' of the output is written to
  * out_peers[r' / rows_per_peer] at local row r' % rows_per_peer (strides args->o_stride, batch and head
  * offsets as usual; args->out is ignored).  out_peers is a host array of n_peers (<= 16) device pointers

@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "mcs_error_string",
     "mcs_gather_attn_fwd",
     "mcs_gather_attn_fwd_sharded",
+    "mcs_dense_attn_fwd",
     "mcs_ulysses_scatter",
     "mcs_group_mass",
     "mcs_topk_select",
@@ -103,6 +104,8 @@ def lib() -> C.CDLL:
     L.mcs_error_string.argtypes = [C.c_int]
     L.mcs_gather_attn_fwd.restype = C.c_int
     L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
+    L.mcs_dense_attn_fwd.restype = C.c_int
+    L.mcs_dense_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
     L.mcs_gather_attn_fwd_sharded.restype = C.c_int
     L.mcs_gather_attn_fwd_sharded.argtypes = [C.POINTER(GatherAttnArgs), C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
                                               C.c_void_p]

@@ -57,9 +57,10 @@ const char* mcs_error_string(int code) {
 }
 
 static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_peers, int n_peers, int rows_per_peer,
-                                void* stream) {
-  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->gi == nullptr || a->status == nullptr)
+                                bool dense, void* stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
+  if (!dense && a->gi == nullptr) return MCS_ERR_NULL_POINTER;
   if (n_peers == 0 && a->out == nullptr) return MCS_ERR_NULL_POINTER;
   if (n_peers > 0) {
     if (out_peers == nullptr) return MCS_ERR_NULL_POINTER;
@@ -70,7 +71,8 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
     }
   }
   if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return MCS_ERR_BAD_SHAPE;
-  if (a->gather_len < 128 || a->gather_len % 128 != 0) return MCS_ERR_BAD_SHAPE;
+  if (!dense && (a->gather_len < 128 || a->gather_len % 128 != 0)) return MCS_ERR_BAD_SHAPE;
+  if (dense && (a->gl != nullptr || a->dtype == MCS_DTYPE_E4M3)) return MCS_ERR_UNSUPPORTED;
   if (a->group_rows < 1 || a->group_rows > 128) return MCS_ERR_BAD_SHAPE;
   if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16 && a->dtype != MCS_DTYPE_E4M3)
     return MCS_ERR_BAD_DTYPE;
@@ -97,6 +99,11 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   }
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.H = a->H; p.D = a->D;
   p.M = (int)groups; p.gather_len = a->gather_len; p.group_rows = a->group_rows;
+  if (dense) {
+    p.dense = 1;
+    p.gi = nullptr;
+    p.gather_len = (a->Sk + 127) / 128 * 128;       // every key tile of the sequence
+  }
   p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
   for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -117,13 +124,17 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
 }
 
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
-  return gather_attn_dispatch(a, nullptr, 0, 0, stream);
+  return gather_attn_dispatch(a, nullptr, 0, 0, false, stream);
+}
+
+int mcs_dense_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
+  return gather_attn_dispatch(a, nullptr, 0, 0, true, stream);
 }
 
 int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* a, void* const* out_peers, int32_t n_peers,
                                 int32_t rows_per_peer, void* stream) {
   if (n_peers < 1) return MCS_ERR_BAD_SHAPE;
-  return gather_attn_dispatch(a, out_peers, n_peers, rows_per_peer, stream);
+  return gather_attn_dispatch(a, out_peers, n_peers, rows_per_peer, false, stream);
 }
 
 int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,

@@ -200,7 +200,7 @@ __device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item)
   const int max_tiles = p.gather_len / kTileN;
   it.T = max_tiles;
   if (p.gl != nullptr) it.T = min(max(p.gl[item], 1), max_tiles);
-  it.gi = p.gi + (size_t)item * p.gather_len;
+  it.gi = p.dense ? nullptr : p.gi + (size_t)item * p.gather_len;
   return it;
 }
 
@@ -333,6 +333,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         tmem_wait_ld();
         tc_fence_before();
         warp_arrive(bar(BAR_S_FREE + buf));
+        if (p.dense && t == it.T - 1) {
+          // dense mode: key positions beyond the sequence end (zero-filled rows of the last tile) get -inf
+          const int rem = p.Sk - t * kTileN - x * 64;      // valid columns of this stream's half
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i >= rem) sc[i] = 0xff800000u;
+        }
         TL(8, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // P[buf] was last read by P V of tile g-2: probe now, wait (if at all) just before the stores
         const bool p_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
@@ -506,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (D == 128) prefetch_l2(res_row + 128);
         }
       }
-      if (item + (int)gridDim.x < n_items) {
+      if (!p.dense && item + (int)gridDim.x < n_items) {
         const uint8_t* gin = reinterpret_cast<const uint8_t*>(p.gi + (size_t)(item + gridDim.x) * p.gather_len);
         const int bytes = p.gather_len * 4;
         for (int off = (pw * 32 + lane) * 128; off < bytes; off += kProducerThreads * 128) prefetch_l2(gin + off);
@@ -546,10 +553,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     auto set_item = [&](Cur& c, const void* tensor, const int64_t* stride) {
       const Item it = decode_item(p, c.item);
       c.T = it.T;
-      c.gi = it.gi + my_row;
+      c.gi = p.dense ? nullptr : it.gi + my_row;
       c.kv = reinterpret_cast<const uint8_t*>(tensor) + kEs * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
     };
-    auto load_idx = [&](const Cur& c) { return __ldg(c.gi + c.t * kTileN); };
+    // dense mode: the "selected" tokens of tile t are simply t*128 .. t*128+127 (rows beyond the end are
+    // clamped here and masked in the softmax)
+    auto load_idx = [&](const Cur& c) { return p.dense ? c.t * kTileN + my_row : __ldg(c.gi + c.t * kTileN); };
 
     // Fill order = consumption order of the MMA warp: K(0), then per tile g: K(g+1), V(g),
     // where g+1 may belong to the next work item (its Q is requested just before its K(0)).

@@ -266,13 +266,13 @@ class TokenSparseCache:
 
 
 def dense_attention_with_lse(q, k, v, scale):
-    """Dense attention output and natural-log LSE on (B,H,L,D) tensors.
+    """Dense attention output and natural-log LSE on (B,H,L,D) tensors: the input of the anchor step.
 
-    The input of the anchor step (the reference calls FA3 here, ops/full_attn.py:88-121).  This is a
-    library call (torch's flash attention), not one of this package's kernels.
+    The reference calls FA3 here (ops/full_attn.py:88-121); this is the package's own attention kernel in
+    dense mode, on strided views of the (B,H,L,D) tensors (no layout copies).
     """
-    out, lse = torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.0, False, False, scale=scale)[:2]
-    return out, lse.float()
+    from mcsparse_b200.kernels.flash_mcsa.ops.full_attn import full_attention_with_lse
+    return full_attention_with_lse(q, k, v, scale)
 
 
 class TokenSparseBackend:
