@@ -462,7 +462,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--chunks", type=int, default=3, help="head chunks of the Ulysses pipeline (N > 1)")
+    ap.add_argument("--chunks", type=int, default=1, help="head chunks of the Ulysses pipeline (N > 1)")
     ap.add_argument("--graph", action="store_true", help="N > 1, fused: replay one captured CUDA graph per step instead of launching eagerly")
     ap.add_argument("--ulysses", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store reshard fused with the attention kernel, or library all-to-alls around it")
