@@ -209,7 +209,7 @@ __device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item)
 // 145-241): logits = (q8 . k8) * scale_qk_log2[b,h,m] in the log2 domain, O * scale_v[b,h]; V is used
 // as it lies in memory (MN-major MMA operand), so neither the Hopper kernel's in-smem transpose nor
 // its d-column pre-permutation exists here.
-template <int D, int kType>
+template <int D, int kType, bool kDense>
 __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAttnParams p) {
   constexpr bool kFp16 = kType == 1;
   constexpr bool kFp8 = kType == 2;
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         tmem_wait_ld();
         tc_fence_before();
         warp_arrive(bar(BAR_S_FREE + buf));
-        if (p.dense && t == it.T - 1) {
+        if (kDense && t == it.T - 1) {
           // dense mode: key positions beyond the sequence end (zero-filled rows of the last tile) get -inf
           const int rem = p.Sk - t * kTileN - x * 64;      // valid columns of this stream's half
 #pragma unroll
@@ -513,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (D == 128) prefetch_l2(res_row + 128);
         }
       }
-      if (!p.dense && item + (int)gridDim.x < n_items) {
+      if (!kDense && item + (int)gridDim.x < n_items) {
         const uint8_t* gin = reinterpret_cast<const uint8_t*>(p.gi + (size_t)(item + gridDim.x) * p.gather_len);
         const int bytes = p.gather_len * 4;
         for (int off = (pw * 32 + lane) * 128; off < bytes; off += kProducerThreads * 128) prefetch_l2(gin + off);
@@ -553,12 +553,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     auto set_item = [&](Cur& c, const void* tensor, const int64_t* stride) {
       const Item it = decode_item(p, c.item);
       c.T = it.T;
-      c.gi = p.dense ? nullptr : it.gi + my_row;
+      c.gi = kDense ? nullptr : it.gi + my_row;
       c.kv = reinterpret_cast<const uint8_t*>(tensor) + kEs * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
     };
     // dense mode: the "selected" tokens of tile t are simply t*128 .. t*128+127 (rows beyond the end are
     // clamped here and masked in the softmax)
-    auto load_idx = [&](const Cur& c) { return p.dense ? c.t * kTileN + my_row : __ldg(c.gi + c.t * kTileN); };
+    auto load_idx = [&](const Cur& c) { return kDense ? c.t * kTileN + my_row : __ldg(c.gi + c.t * kTileN); };
 
     // Fill order = consumption order of the MMA warp: K(0), then per tile g: K(g+1), V(g),
     // where g+1 may belong to the next work item (its Q is requested just before its K(0)).
@@ -920,10 +920,10 @@ int num_sms() {
   return cached[dev];
 }
 
-template <int D, int kType>
+template <int D, int kType, bool kDense = false>
 int launch(const GatherAttnParams& p, cudaStream_t stream) {
   using L = Smem<D * (kType == 2 ? 1 : 2), kType == 2 ? 256 * D : 0>;
-  auto kern = gather_attn_kernel<D, kType>;
+  auto kern = gather_attn_kernel<D, kType, kDense>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return -8;
   const long long items = (long long)p.B * p.H * p.M;
@@ -935,6 +935,12 @@ int launch(const GatherAttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream) {
+  if (p.dense) {
+    // dense mode is its own instantiation so that the sparse kernel's inner loops carry none of it
+    if (p.D == 128) return fp16 ? launch<128, 1, true>(p, stream) : launch<128, 0, true>(p, stream);
+    if (p.D == 64) return fp16 ? launch<64, 1, true>(p, stream) : launch<64, 0, true>(p, stream);
+    return -3;
+  }
   if (p.D == 128) return fp16 ? launch<128, 1>(p, stream) : launch<128, 0>(p, stream);
   if (p.D == 64) return fp16 ? launch<64, 1>(p, stream) : launch<64, 0>(p, stream);
   return -3;
