@@ -239,6 +239,11 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.2)
+    # the attention kernel reports the cycles and nanoseconds of its own tile loop (first CTA): the SM clock
+    # under the timed load itself
+    import ctypes
+    kclk = torch.zeros(3, dtype=torch.int64, device=dev)
+    _lib.lib().mcs_set_clock_buffer(ctypes.c_void_p(kclk.data_ptr()))
     # ---- device-resident timing: whole region + per-launch kernel time on the launching stream
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
@@ -250,7 +255,6 @@ def run_ours(args):
     # counting SM cycles against the nanosecond timer; nvidia-smi's poll cannot resolve a region of a
     # few milliseconds
     probe = torch.zeros(2, dtype=torch.int64, device=dev)
-    import ctypes
     _lib.lib().mcs_sm_clock_probe(ctypes.c_void_p(probe.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
@@ -259,6 +263,9 @@ def run_ours(args):
     if clocks is not None:
         pc, pn = int(probe[0]), int(probe[1])
         clocks["sm_mhz_probe_after_timed_region"] = round(pc * 1000.0 / pn, 1) if pn > 0 else None
+        kc, kn = int(kclk[0]), int(kclk[1])
+        clocks["sm_mhz_in_kernel_last_timed_launch"] = round(kc * 1000.0 / kn, 1) if kn > 0 else None
+    _lib.lib().mcs_set_clock_buffer(None)
     _lib.check_status(dev, "bench timed region")
 
     # ---- end to end through the public entry point with host buffers

@@ -255,6 +255,15 @@ int mcs_perm_invert(const void* x, void* out, const int64_t* perm, int32_t BH, i
  */
 int mcs_sm_clock_probe(int64_t* out2, void* stream);
 
+/*
+ * Clock telemetry of the attention kernel (no reference counterpart; measurement aid).  After this call
+ * every attention launch of this process writes {SM cycles, nanoseconds, KV tiles} of its first CTA's tile
+ * loop to buf3[0..2] (device memory, three int64; pass NULL to switch it off): cycles * 1000 / nanoseconds
+ * is the SM clock in MHz under the kernel's own load.  Process-wide and not thread-safe, like the
+ * reference's module-global statistics.
+ */
+void mcs_set_clock_buffer(int64_t* buf3);
+
 #ifdef __cplusplus
 }
 #endif

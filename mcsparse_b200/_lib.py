@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "mcs_perm_apply",
     "mcs_perm_invert",
     "mcs_sm_clock_probe",
+    "mcs_set_clock_buffer",
 )
 
 
@@ -112,6 +113,8 @@ def lib() -> C.CDLL:
     L.mcs_ulysses_scatter.restype = C.c_int
     L.mcs_ulysses_scatter.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int64, C.c_int64, C.c_void_p]
+    L.mcs_set_clock_buffer.restype = None
+    L.mcs_set_clock_buffer.argtypes = [C.c_void_p]
     L.mcs_sm_clock_probe.restype = C.c_int
     L.mcs_sm_clock_probe.argtypes = [C.c_void_p, C.c_void_p]
     L.mcs_group_mass.restype = C.c_int

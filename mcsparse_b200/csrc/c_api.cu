@@ -23,12 +23,16 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
-#if defined(MCS_TRACE) || defined(MCS_CLK)
+#if defined(MCS_TRACE)
 static long long* g_trace = nullptr;
 extern "C" void mcs_debug_set_trace(long long* t) { g_trace = t; }
 #endif
 
+static long long* g_clock_out = nullptr;
+
 extern "C" {
+
+void mcs_set_clock_buffer(int64_t* buf3) { g_clock_out = reinterpret_cast<long long*>(buf3); }
 
 int mcs_sm_clock_probe(int64_t* out2, void* stream) {
   if (out2 == nullptr) return MCS_ERR_NULL_POINTER;
@@ -107,7 +111,8 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
   for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#if defined(MCS_TRACE) || defined(MCS_CLK)
+  p.clock_out = g_clock_out;
+#if defined(MCS_TRACE)
   p.trace = g_trace;
 #endif
 

@@ -297,11 +297,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     bool ok = true;
     TR_DECL;
     TR_BEGIN();
-#if defined(MCS_CLK)
-    // diagnostics: SM clocks and nanoseconds this role of CTA 0 ran (the SM clock under load)
-    const long long clk_c0 = clock64();
-    const unsigned long long clk_g0 = globaltimer_ns();
-#endif
 
     constexpr int kHalf = D / 2;                 // output columns whose accumulator this stream rescales
     bool s_ready = false;       // next tile's score barrier was already complete when probed
@@ -466,13 +461,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         item += gridDim.x;
       }
     }
-#if defined(MCS_CLK)
-    if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) {
-      p.trace[0] = clock64() - clk_c0;
-      p.trace[1] = static_cast<long long>(globaltimer_ns() - clk_g0);
-      p.trace[2] = g;
-    }
-#endif
     TR_FLUSH(x, lane == 0 && (warp & 3) == 0);
     tc_fence_before();
   } else if (warp < kMmaWarp) {
@@ -772,6 +760,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       TR_DECL;
       TR_BEGIN();
       int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
+      // optional telemetry (mcs_set_clock_buffer): SM cycles and nanoseconds this CTA's tile loop ran, i.e.
+      // the SM clock under the kernel's own load, which no host-side poll can resolve
+      const bool telemetry = p.clock_out != nullptr && blockIdx.x == 0;
+      long long clk_c0 = 0;
+      unsigned long long clk_g0 = 0;
+      if (telemetry) { clk_c0 = clock64(); clk_g0 = globaltimer_ns(); }
 #pragma unroll 1
       while (item < n_items) {
         const int qbuf = ic & 1, buf = g & 1;
@@ -819,6 +813,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           ++ic;
           if (item < n_items) T = decode_item(p, item).T;
         }
+      }
+      if (telemetry && lane == 0) {
+        p.clock_out[0] = clock64() - clk_c0;
+        p.clock_out[1] = static_cast<long long>(globaltimer_ns() - clk_g0);
+        p.clock_out[2] = g;
       }
       TR_END(0);
       TR_FLUSH(3, lane == 0);

@@ -22,6 +22,7 @@ struct GatherAttnParams {
   int B, Sq, Sk, H, D, M, gather_len, group_rows;
   float scale_log2;  // softmax_scale * log2(e)
   long long* trace;  // diagnostics builds only (MCS_TRACE): per-role event clocks of CTA 0
+  long long* clock_out;  // optional: {SM cycles, nanoseconds, tiles} of CTA 0's tile loop (mcs_set_clock_buffer)
   // sequence-sharded output (Ulysses): row r' of the output goes to out_peer[r' / out_rows_per_peer] at local
   // row r' % out_rows_per_peer (peer or local memory alike)
   void* out_peer[16];
