@@ -49,8 +49,14 @@
 // Math follows the reference's Hopper kernel
 // (mcsparse/kernels/flash_mcsa/ops/flash_sparse_attn/cute/flash_fwd_sm90.py:1005-1340,
 // softmax.py:126-227); gather addressing follows topk_gather_kv.py:351-445.
+#include <cuda.h>
+#include <cudaTypedefs.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include <cstring>
 
 #include "kernels.cuh"
 #include "ptx.cuh"
@@ -210,7 +216,10 @@ __device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item)
 // as it lies in memory (MN-major MMA operand), so neither the Hopper kernel's in-smem transpose nor
 // its d-column pre-permutation exists here.
 template <int D, int kType, bool kDense>
-__global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAttnParams p) {
+__global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAttnParams p,
+                                                                    const __grid_constant__ DenseTileMaps maps) {
+  // dense mode with valid tensor maps: K/V tiles arrive by TMA (one elected thread, two 16 KB boxes per tile)
+  const bool use_tma = kDense && maps.valid != 0;
   constexpr bool kFp16 = kType == 1;
   constexpr bool kFp8 = kType == 2;
   constexpr int kEs = kFp8 ? 1 : 2;              // bytes per Q/K/V element
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
   // ---- setup
   if (tid == 0) {
     for (int i = 0; i < kRing; ++i) {
-      mbar_init(bar(BAR_FULL + i), kProducerThreads);
+      mbar_init(bar(BAR_FULL + i), use_tma ? 1 : kProducerThreads);
       mbar_init(bar(BAR_EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -517,6 +526,33 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 
     int tl_k = 0, tl_v = 0;   // diagnostics: CTA-global tile numbers of the K and V cursors
     (void)tl_k; (void)tl_v;
+    // per-item constants of a cursor
+    struct Cur {
+      int item, ic, t, T, b, h;
+      const int32_t* gi;     // this thread's entry of tile 0
+      const uint8_t* kv;     // K or V base of (b, h) + chunk offset of this lane
+    };
+    const bool tma_leader = elect_one();
+    auto load_tile_tma = [&](const Cur& c, bool is_v) {
+      // dense mode: the tile is 128 consecutive key rows of one (batch, head): kBlocks TMA boxes of 128 rows x
+      // 128 bytes, issued by one thread of producer warp 0; rows beyond the sequence end arrive as zeros
+      if (pw == 0) {
+        if (wrapped) ok = ok && mbar_wait(bar(BAR_EMPTY + slot), slot_phase ^ 1, p.status, 20);
+        if (!ok) return;
+        if (tma_leader) {
+          mbar_arrive_expect_tx(bar(BAR_FULL + slot), L::kTileBytes);
+          const void* map = is_v ? static_cast<const void*>(maps.v) : static_cast<const void*>(maps.k);
+          int co[4] = {0, 0, 0, 0};
+          co[is_v ? maps.v_pos_h : maps.k_pos_h] = c.h;
+          co[is_v ? maps.v_pos_row : maps.k_pos_row] = c.t * kTileN;
+          co[is_v ? maps.v_pos_b : maps.k_pos_b] = c.b;
+#pragma unroll
+          for (int cb = 0; cb < L::kBlocks; ++cb)
+            tma_load_4d(sRing(slot) + cb * 16384, map, cb * (128 / kEs), co[1], co[2], co[3], bar(BAR_FULL + slot));
+        }
+      }
+      if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
+    };
     auto load_tile = [&](const uint8_t* lane_src, size_t row_bytes, int idx, bool is_v) {
       TR_END(0);
       if (wrapped) ok = ok && mbar_wait(bar(BAR_EMPTY + slot), slot_phase ^ 1, p.status, 20);
@@ -532,15 +568,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
     };
 
-    // per-item constants of a cursor
-    struct Cur {
-      int item, ic, t, T;
-      const int32_t* gi;     // this thread's entry of tile 0
-      const uint8_t* kv;     // K or V base of (b, h) + chunk offset of this lane
-    };
     auto set_item = [&](Cur& c, const void* tensor, const int64_t* stride) {
       const Item it = decode_item(p, c.item);
       c.T = it.T;
+      c.b = it.b;
+      c.h = it.h;
       c.gi = kDense ? nullptr : it.gi + my_row;
       c.kv = reinterpret_cast<const uint8_t*>(tensor) + kEs * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
     };
@@ -552,12 +584,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     // where g+1 may belong to the next work item (its Q is requested just before its K(0)).
     // The indices of the next K tile are fetched one step ahead of their use.
     if (blockIdx.x < n_items) {
-      Cur kc{static_cast<int>(blockIdx.x), 0, 0, 0, nullptr, nullptr}, vc = kc;
+      Cur kc{static_cast<int>(blockIdx.x), 0, 0, 0, 0, 0, nullptr, nullptr}, vc = kc;
       set_item(kc, p.k, p.k_stride);
       set_item(vc, p.v, p.v_stride);
       enter_item(kc.item, kc.ic);
       int idx_k = load_idx(kc);
-      load_tile(kc.kv, k_row, idx_k, false);
+      if (use_tma) load_tile_tma(kc, false); else load_tile(kc.kv, k_row, idx_k, false);
       int idx_v = idx_k;
       auto advance_k = [&]() {
         if (++kc.t >= kc.T) {
@@ -577,7 +609,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         if (had_k) {
           if (kc.t == 0) enter_item(kc.item, kc.ic);
           if (!ok) break;
-          load_tile(kc.kv, k_row, idx_cur, false);
+          if (use_tma) load_tile_tma(kc, false); else load_tile(kc.kv, k_row, idx_cur, false);
           if (!ok) break;
           advance_k();
           have_k = kc.item < n_items;
@@ -587,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           // no K entry in this (final) step: skip its ring number so that V(g) is always entry 2g+2
           if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
         }
-        load_tile(vc.kv, v_row, idx_v, true);
+        if (use_tma) load_tile_tma(vc, true); else load_tile(vc.kv, v_row, idx_v, true);
         if (!ok) break;
         idx_v = idx_cur;                           // V(g+1) uses the indices of K(g+1)
         if (++vc.t >= vc.T) {
@@ -919,6 +951,57 @@ int num_sms() {
   return cached[dev];
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (no link-time dependency on the driver)
+PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled>(f);
+  }();
+  return fn;
+}
+
+// 4-D tensor map of a (B, S, H, D) tensor of 16-bit elements with element strides {batch, row, head}: D innermost,
+// then head / row / batch in the order of ascending stride (dimensions of extent 1 last, packed).  Box: 64
+// elements (128 bytes, the swizzle span) x 128 rows.  Returns false if the layout cannot be described.
+bool encode_tile_map(const void* base, const int64_t* stride, int B, int S, int H, int D, unsigned long long* out,
+                     int& pos_h, int& pos_row, int& pos_b) {
+  PFN_cuTensorMapEncodeTiled enc = tensor_map_encoder();
+  if (enc == nullptr) return false;
+  struct Dim { int which; unsigned long long extent; long long stride_bytes; };
+  Dim d[3] = {{0, (unsigned long long)H, 2 * stride[2]}, {1, (unsigned long long)S, 2 * stride[1]}, {2, (unsigned long long)B, 2 * stride[0]}};
+  std::stable_sort(d, d + 3, [](const Dim& a, const Dim& b) {
+    const bool a1 = a.extent == 1, b1 = b.extent == 1;
+    if (a1 != b1) return b1;                     // extent-1 dimensions go last
+    return a.stride_bytes < b.stride_bytes;
+  });
+  unsigned long long prev_end = (unsigned long long)D * 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, 0, 0, 0};
+  cuuint64_t strides[3];
+  cuuint32_t box[4] = {64, 1, 1, 1}, estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i) {
+    long long sb = d[i].stride_bytes;
+    if (d[i].extent == 1) sb = (long long)prev_end;           // any valid stride: the coordinate is always 0
+    if (sb <= 0 || (sb % 16) != 0 || (unsigned long long)sb < prev_end) return false;   // overlapping or misaligned
+    dims[i + 1] = d[i].extent;
+    strides[i] = (cuuint64_t)sb;
+    prev_end = (unsigned long long)sb * d[i].extent;
+    if (d[i].which == 0) pos_h = i + 1;
+    if (d[i].which == 1) { pos_row = i + 1; box[i + 1] = 128; }
+    if (d[i].which == 2) pos_b = i + 1;
+  }
+  CUtensorMap tm;
+  const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+  memcpy(out, &tm, 128);
+  return true;
+}
+
 template <int D, int kType, bool kDense = false>
 int launch(const GatherAttnParams& p, cudaStream_t stream) {
   using L = Smem<D * (kType == 2 ? 1 : 2), kType == 2 ? 256 * D : 0>;
@@ -927,7 +1010,13 @@ int launch(const GatherAttnParams& p, cudaStream_t stream) {
   if (e != cudaSuccess) return -8;
   const long long items = (long long)p.B * p.H * p.M;
   const int grid = (int)(items < num_sms() ? items : num_sms());
-  kern<<<grid, kThreads, L::kDynamic, stream>>>(p);
+  DenseTileMaps maps{};
+  if (kDense) {
+    // K/V tiles of the dense mode are consecutive rows: load them with TMA when the layout allows it
+    maps.valid = encode_tile_map(p.k, p.k_stride, p.B, p.Sk, p.H, D, maps.k, maps.k_pos_h, maps.k_pos_row, maps.k_pos_b) &&
+                 encode_tile_map(p.v, p.v_stride, p.B, p.Sk, p.H, D, maps.v, maps.v_pos_h, maps.v_pos_row, maps.v_pos_b);
+  }
+  kern<<<grid, kThreads, L::kDynamic, stream>>>(p, maps);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

@@ -31,6 +31,17 @@ struct GatherAttnParams {
   int out_rows_per_peer;
 };
 
+// Tensor maps of K and V for the dense mode (TMA tile loads of 128 contiguous key rows): 4-D maps with the
+// head dimension innermost and (head, row, batch) in the order of ascending stride; pos_* say at which
+// coordinate position each of them sits (1..3).  Opaque 128-byte blobs (CUtensorMap), 64-byte aligned.
+struct alignas(64) DenseTileMaps {
+  unsigned long long k[16];
+  unsigned long long v[16];
+  int k_pos_h, k_pos_row, k_pos_b;
+  int v_pos_h, v_pos_row, v_pos_b;
+  int valid;     // 0: maps not built, the dense mode gathers rows with cp.async like the sparse mode
+};
+
 struct GroupMassParams {
   const void* q;        // (B, Lq, H, D) strided
   const void* k;        // (B, Lk, H, D) strided

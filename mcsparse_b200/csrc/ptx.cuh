@@ -163,6 +163,18 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// mbarrier: one arrival that also announces `bytes` of asynchronous (TMA) writes to come
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// TMA tile load of a 4-D tensor map box into shared memory; completion is counted in bytes on `bar`.
+// c0 is the innermost (contiguous) coordinate: c0 * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tensor_map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 // True in exactly one lane of a converged warp.  The MMA-issuing warps run their loops converged,
 // with warp-uniform operands, and predicate only the tcgen05 instruction itself on this: issued from
 // a lane-dependent branch instead, every operand has to be moved from per-thread to uniform registers
