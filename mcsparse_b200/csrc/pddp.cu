@@ -235,59 +235,62 @@ __global__ void __launch_bounds__(kGramThreads, 1) pddp_gram_kernel(PddpParams p
 // ------------------------------------------------------------------------------------------
 // power: v[bh][node] = principal direction of the node (pow_iters normalised mat-vecs)
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ float block_sum_128(float v, float* red) {
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int w = threadIdx.x >> 5;
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[w] = v;
-  __syncthreads();
-  return (red[0] + red[1]) + (red[2] + red[3]);
-}
 
-__global__ void __launch_bounds__(128, 1) pddp_power_kernel(PddpParams p, int lv, int nodes, const float* v0) {
+// 512 threads: thread (d, q) = (tid & 127, tid >> 7) owns element d and the Gram rows e = q (mod 4).  The
+// arithmetic is exactly that of a 128-thread version with four accumulators per element (a_q summed over
+// e = q, q+4, ... in increasing order, combined as (a0 + a1) + (a2 + a3)), so results do not depend on the
+// thread count; four times the threads only shorten the dependent load and FMA chains, which is what the
+// deep levels with thousands of small nodes are bound by.
+__global__ void __launch_bounds__(512, 1) pddp_power_kernel(PddpParams p, int lv, int nodes, const float* v0) {
   extern __shared__ __align__(16) float sm[];
   float* G = sm;                 // 128 x 128, symmetric
   float* vec = sm + 128 * 128;   // 128
-  float* red = vec + 128;        // 4
+  float* partial = vec + 128;    // 4 x 128
+  float* red = partial + 512;    // 4
   const LevelTables T = level_tables(p.tables, lv, p.table_stride);
-  const int node = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+  const int node = blockIdx.x, bh = blockIdx.y, d = threadIdx.x & 127, q = threadIdx.x >> 7;
   const int size = T.node_size[node];
   const int item0 = T.node_item0[node];
   const int n_items = (size + kChunkRows - 1) / kChunkRows;
   const float* part = p.partial + ((size_t)bh * p.max_items + item0) * kPartialFloats;
-  // fixed-order reduction of the partial Gram matrices; thread d owns row d
+  // fixed-order reduction of the partial Gram matrices
   float s_d = 0.f;
   for (int it = 0; it < n_items; ++it) s_d += part[(size_t)it * kPartialFloats + 128 * 128 + d];
-  vec[d] = s_d;
+  if (q == 0) vec[d] = s_d;
   __syncthreads();
   const float inv_n = 1.f / (float)size;
-  for (int e = 0; e < 128; ++e) {
+  for (int e = q; e < 128; e += 4) {
     float g = 0.f;
     for (int it = 0; it < n_items; ++it) g += part[(size_t)it * kPartialFloats + (size_t)e * 128 + d];   // G[e][d], coalesced
     G[e * 128 + d] = g - vec[e] * s_d * inv_n;
   }
   __syncthreads();
+  // sum over the 128 elements, identical in all four thread groups: warp sums, then (r0 + r1) + (r2 + r3)
+  auto sum_128 = [&](float x) {
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    __syncthreads();
+    if (q == 0 && (threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+    __syncthreads();
+    return (red[0] + red[1]) + (red[2] + red[3]);
+  };
   const bool live = d < p.D;
   float v = live ? v0[((size_t)bh * nodes + node) * p.D + d] : 0.f;
-  float nrm = sqrtf(block_sum_128(v * v, red));
+  float nrm = sqrtf(sum_128(v * v));
   v /= fmaxf(nrm, 1e-12f);
   for (int iter = 0; iter < p.pow_iters; ++iter) {
     __syncthreads();
-    vec[d] = v;
+    if (q == 0) vec[d] = v;
     __syncthreads();
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    float a = 0.f;
 #pragma unroll 8
-    for (int e = 0; e < 128; e += 4) {            // G symmetric: read G[e][d] (conflict-free) for (G v)[d]
-      a0 += G[e * 128 + d] * vec[e];
-      a1 += G[(e + 1) * 128 + d] * vec[e + 1];
-      a2 += G[(e + 2) * 128 + d] * vec[e + 2];
-      a3 += G[(e + 3) * 128 + d] * vec[e + 3];
-    }
-    v = (a0 + a1) + (a2 + a3);
-    nrm = sqrtf(block_sum_128(v * v, red));
+    for (int e = q; e < 128; e += 4) a += G[e * 128 + d] * vec[e];     // G symmetric: G[e][d], conflict-free
+    partial[q * 128 + d] = a;
+    __syncthreads();
+    v = (partial[d] + partial[128 + d]) + (partial[256 + d] + partial[384 + d]);
+    nrm = sqrtf(sum_128(v * v));
     v /= fmaxf(nrm, 1e-12f);
   }
-  p.dir[((size_t)bh * p.dir_nodes + node) * 128 + d] = v;
+  if (q == 0) p.dir[((size_t)bh * p.dir_nodes + node) * 128 + d] = v;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -299,43 +302,63 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+constexpr int kProjRows = 8;     // rows per warp: eight independent row loads in flight per lane
+
 template <bool kFp16>
 __global__ void __launch_bounds__(256) pddp_project_kernel(PddpParams p, int lv, int nodes, int pad, const int* perm_in,
                                                            float* proj_out) {
   const LevelTables T = level_tables(p.tables, lv, p.table_stride);
   const int bh = blockIdx.y;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  // one warp per slot of the padded key array: slot = node * pad + r
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  // one warp per kProjRows consecutive slots of the padded key array (slot = node * pad + r); pad is a
+  // multiple of kProjRows, so the slots of a warp belong to one node
   const long long total = (long long)nodes * pad;
-  if (warp >= total) return;
-  const int node = warp / pad, r = warp % pad;
+  const long long slot0 = warp * kProjRows;
+  if (slot0 >= total) return;
+  const int node = (int)(slot0 / pad), r0 = (int)(slot0 % pad);
   unsigned long long* keys = p.keys + (size_t)bh * p.key_stride;
-  if (r >= T.node_size[node]) {
-    if (lane == 0) keys[warp] = 0xFFFFFFFFFFFFFFFFull;           // padding sorts last
-    return;
+  const int nsize = T.node_size[node];
+  const int pos0 = T.node_start[node] + r0;
+  const bool lane_live = lane * 4 < p.D;
+  float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (lane_live) vv = *reinterpret_cast<const float4*>(p.dir + ((size_t)bh * p.dir_nodes + node) * 128 + lane * 4);
+  // row ids of this warp's slots (lane i holds slot i), then all row loads before any arithmetic
+  int my_id = -1;
+  if (lane < kProjRows && r0 + lane < nsize) my_id = perm_in[(size_t)bh * p.N + pos0 + lane];
+  uint2 w[kProjRows];
+#pragma unroll
+  for (int i = 0; i < kProjRows; ++i) {
+    const int id = __shfl_sync(0xffffffffu, my_id, i);
+    w[i] = make_uint2(0u, 0u);
+    if (id >= 0 && lane_live)
+      w[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(p.x) +
+                                            2 * ((size_t)bh * p.x_stride_bh + (size_t)id * p.x_stride_row) + lane * 8);
   }
-  const int pos = T.node_start[node] + r;
-  const int id = perm_in[(size_t)bh * p.N + pos];
-  const uint8_t* row = reinterpret_cast<const uint8_t*>(p.x) + 2 * ((size_t)bh * p.x_stride_bh + (size_t)id * p.x_stride_row);
-  const float* v = p.dir + ((size_t)bh * p.dir_nodes + node) * 128;
-  float acc = 0.f;
-  if (lane * 4 < p.D) {
-    const uint2 w = *reinterpret_cast<const uint2*>(row + lane * 8);      // 4 elements
-    float2 a, b;
-    if (kFp16) {
-      a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-      b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-    } else {
-      a = make_float2(bf16_lo(w.x), bf16_hi(w.x));
-      b = make_float2(bf16_lo(w.y), bf16_hi(w.y));
+#pragma unroll
+  for (int i = 0; i < kProjRows; ++i) {
+    float acc = 0.f;
+    if (lane_live) {
+      float2 a, b;
+      if (kFp16) {
+        a = __half22float2(*reinterpret_cast<const __half2*>(&w[i].x));
+        b = __half22float2(*reinterpret_cast<const __half2*>(&w[i].y));
+      } else {
+        a = make_float2(bf16_lo(w[i].x), bf16_hi(w[i].x));
+        b = make_float2(bf16_lo(w[i].y), bf16_hi(w[i].y));
+      }
+      acc = fmaf(a.x, vv.x, fmaf(a.y, vv.y, fmaf(b.x, vv.z, b.y * vv.w)));
     }
-    const float4 vv = *reinterpret_cast<const float4*>(v + lane * 4);
-    acc = fmaf(a.x, vv.x, fmaf(a.y, vv.y, fmaf(b.x, vv.z, b.y * vv.w)));
-  }
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
-    keys[warp] = ((unsigned long long)float_key(acc) << 32) | (unsigned)r;
-    if (proj_out != nullptr) proj_out[(size_t)bh * p.N + pos] = acc;
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const int r = r0 + i;
+      if (r >= nsize) {
+        keys[slot0 + i] = 0xFFFFFFFFFFFFFFFFull;               // padding sorts last
+      } else {
+        keys[slot0 + i] = ((unsigned long long)float_key(acc) << 32) | (unsigned)r;
+        if (proj_out != nullptr) proj_out[(size_t)bh * p.N + pos0 + i] = acc;
+      }
+    }
   }
 }
 
@@ -495,7 +518,7 @@ int launch_pddp(const PddpArgs& a, cudaStream_t stream) {
     pddp_tables_kernel<<<1, 1, 0, stream>>>(N, C, p.tables, pl.levels, pl.table_stride);
     auto gram = a.fp16 ? pddp_gram_kernel<true> : pddp_gram_kernel<false>;
     if (cudaFuncSetAttribute(gram, cudaFuncAttributeMaxDynamicSharedMemorySize, kGramSmem) != cudaSuccess) return -8;
-    const int power_smem = (128 * 128 + 128 + 8) * sizeof(float);
+    const int power_smem = (128 * 128 + 128 + 512 + 8) * sizeof(float);
     if (cudaFuncSetAttribute(pddp_power_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, power_smem) != cudaSuccess) return -8;
     const float* v0 = a.start_vectors;
     for (int lv = 0; lv < pl.levels; ++lv) {
@@ -503,11 +526,11 @@ int launch_pddp(const PddpArgs& a, cudaStream_t stream) {
       if (a.perm_levels != nullptr)
         cudaMemcpyAsync(a.perm_levels + (size_t)lv * total, perm_a, total * sizeof(int), cudaMemcpyDeviceToDevice, stream);
       gram<<<dim3(ls.items, BH), kGramThreads, kGramSmem, stream>>>(p, lv, perm_a);
-      pddp_power_kernel<<<dim3(ls.nodes, BH), 128, power_smem, stream>>>(p, lv, ls.nodes, v0);
+      pddp_power_kernel<<<dim3(ls.nodes, BH), 512, power_smem, stream>>>(p, lv, ls.nodes, v0);
       v0 += (size_t)BH * ls.nodes * a.D;
       const long long slots = (long long)ls.nodes * ls.pad;
       float* proj = a.proj_levels != nullptr ? a.proj_levels + (size_t)lv * total : nullptr;
-      const unsigned pgrid = (unsigned)((slots * 32 + 255) / 256);
+      const unsigned pgrid = (unsigned)((slots / kProjRows * 32 + 255) / 256);
       if (a.fp16) pddp_project_kernel<true><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
       else pddp_project_kernel<false><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
       // bitonic sort of every segment of `pad` keys
