@@ -46,11 +46,6 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Arrive without release semantics: does not wait for this thread's outstanding global loads and
-// stores.  Only for barriers that order tensor-memory traffic (ordered by the tcgen05 fences).
-__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
-  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -81,21 +76,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// try_wait with an explicit upper bound (nanoseconds) on how long the hardware may suspend
-// the thread: sleeps instead of spinning, but comes back in time to look at other barriers.
-__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t max_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(max_ns)
-      : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
@@ -132,16 +112,6 @@ __device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, i
   return false;
 }
 
-// Register re-allocation between warp-specialised roles.  Every warp of a warpgroup
-// (4 consecutive warps) must execute the same instruction.
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
 
 // ----------------------------------------------------------------------------
 // cp.async (16-byte, L2-only) and fences
@@ -204,11 +174,6 @@ __device__ __forceinline__ bool named_bar_red_or(int id, int nthreads, bool pred
       : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
       : "memory");
   return r != 0;
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 // Make generic-proxy shared-memory writes visible to the async proxy
 // (tcgen05.mma reads its operands through the async proxy).
@@ -278,25 +243,6 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
       "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
       : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
-      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -390,14 +336,6 @@ __device__ __forceinline__ void sts_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// 16-byte read-only global load that does not allocate in L1 (streamed once).
-__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
-  uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "l"(p));
-  return r;
-}
 
 // ----------------------------------------------------------------------------
 // Small math helpers
@@ -441,21 +379,6 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
       : "=r"(r)
       : "f"(a), "f"(b), "f"(c), "f"(d));
   return r;
-}
-// four e4m3 bytes -> four floats
-__device__ __forceinline__ void unpack_e4m3x4(uint32_t u, float (&f)[4]) {
-  uint32_t h0, h1;
-  asm("{\n\t"
-      ".reg .b16 lo, hi;\n\t"
-      "mov.b32 {lo, hi}, %2;\n\t"
-      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
-      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t"
-      "}\n"
-      : "=r"(h0), "=r"(h1)
-      : "r"(u));
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h0));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&h1));
-  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
