@@ -474,13 +474,12 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     tc_fence_before();
   } else if (warp < kMmaWarp) {
     // =====================================================================
-    // producers: K/V/Q row gathers, and the epilogue of every finished item.
+    // producers: K/V/Q row gathers.
     //
-    // These four warps own all global-memory traffic of the CTA.  The softmax warps never
-    // use the load/store unit in steady state, so they are never queued behind the hundreds
-    // of cp.async that are in flight.  Producer warp pw gathers tile rows 32*pw..+31 and, in
-    // the epilogue, owns TMEM lanes 32*pw..+31 (its own sub-partition): one query row per
-    // thread in both jobs.
+    // Producer warp pw gathers tile rows 32*pw..+31 of every K, V and Q tile with 16-byte cp.async (the
+    // softmax warps never use the load/store unit, so they are never queued behind the hundreds of copies
+    // in flight).  In the dense mode with tensor maps one elected thread of warp 0 issues the K/V tiles as
+    // TMA boxes instead and the four warps only gather Q.
     // =====================================================================
     const int pw = warp - kProducerWarp0;
     const int row0 = pw * kRowsPerProducerWarp;
