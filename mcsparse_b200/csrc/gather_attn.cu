@@ -493,8 +493,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     TR_BEGIN();
 
     auto enter_item = [&](int item, int ic) {
-      // called once per item when the K cursor reaches it: request Q, remember epilogue pointers,
-      // warm L2 for this item's residual and for the next item's indices
+      // called once per item when the K cursor reaches it: request Q, warm L2 for this item's residual
+      // (read by the epilogue warps later) and for the next item's indices
       const Item it = decode_item(p, item);
       const int qbuf = ic & 1;
       int src_row = -1;
