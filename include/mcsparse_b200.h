@@ -100,6 +100,17 @@ typedef struct mcs_gather_attn_args {
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* args, void* stream);
 
 /*
+ * Residual construction of the anchor step in one pass: out = residual - attention, where args->residual
+ * (required) holds the dense attention output in (B, H, Sq, D) layout and the attention is the sparse
+ * attention defined above; fp32 subtraction, one rounding.  The result is what later reuse steps pass back
+ * as `residual`.
+ *
+ * Replaces: the sparse pass followed by the elementwise `out_full - out_sparse` of
+ * mcsparse/kernels/flash_mcsa/token_sparse.py:1209-1216.
+ */
+int mcs_gather_attn_residual_fwd(const mcs_gather_attn_args* args, void* stream);
+
+/*
  * Dense attention with log-sum-exp through the same kernel: every query group attends to all Sk keys
  * (args->gi, gl, gather_len are ignored; bf16 / fp16 only; the part of the last 128-key tile beyond Sk is
  * masked).  residual, perm and lse work as above.  This is the input of the anchor step: the dense output

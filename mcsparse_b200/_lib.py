@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "mcs_gather_attn_fwd",
     "mcs_gather_attn_fwd_sharded",
     "mcs_dense_attn_fwd",
+    "mcs_gather_attn_residual_fwd",
     "mcs_ulysses_scatter",
     "mcs_group_mass",
     "mcs_topk_select",
@@ -105,6 +106,8 @@ def lib() -> C.CDLL:
     L.mcs_error_string.argtypes = [C.c_int]
     L.mcs_gather_attn_fwd.restype = C.c_int
     L.mcs_gather_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
+    L.mcs_gather_attn_residual_fwd.restype = C.c_int
+    L.mcs_gather_attn_residual_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
     L.mcs_dense_attn_fwd.restype = C.c_int
     L.mcs_dense_attn_fwd.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
     L.mcs_gather_attn_fwd_sharded.restype = C.c_int

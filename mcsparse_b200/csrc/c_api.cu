@@ -61,7 +61,7 @@ const char* mcs_error_string(int code) {
 }
 
 static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_peers, int n_peers, int rows_per_peer,
-                                bool dense, void* stream) {
+                                bool dense, void* stream, bool negate = false) {
   if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
   if (!dense && a->gi == nullptr) return MCS_ERR_NULL_POINTER;
@@ -108,6 +108,8 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
     p.gi = nullptr;
     p.gather_len = (a->Sk + 127) / 128 * 128;       // every key tile of the sequence
   }
+  if (negate && a->residual == nullptr) return MCS_ERR_NULL_POINTER;
+  p.out_sign = negate ? -1.f : 1.f;
   p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
   for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -130,6 +132,10 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
 
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
   return gather_attn_dispatch(a, nullptr, 0, 0, false, stream);
+}
+
+int mcs_gather_attn_residual_fwd(const mcs_gather_attn_args* a, void* stream) {
+  return gather_attn_dispatch(a, nullptr, 0, 0, false, stream, true);
 }
 
 int mcs_dense_attn_fwd(const mcs_gather_attn_args* a, void* stream) {

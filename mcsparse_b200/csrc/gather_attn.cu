@@ -713,7 +713,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       // both streams' partial sums are relative to the same (shared) row maximum
       const float m_all = stats[256 + r_in];
       const float l_all = stats[r_in] + stats[128 + r_in];
-      const float w = vscale / l_all;
+      const float w = p.out_sign * vscale / l_all;          // out_sign -1: out = residual - attention
       const uint32_t tO = tmem + kColO + lane_addr;
       const uint32_t my_row = st + lane * kRowBytes;
       cp_async_wait_all();

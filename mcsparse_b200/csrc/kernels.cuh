@@ -26,6 +26,7 @@ struct GatherAttnParams {
   // sequence-sharded output (Ulysses): row r' of the output goes to out_peer[r' / out_rows_per_peer] at local
   // row r' % out_rows_per_peer (peer or local memory alike)
   void* out_peer[16];
+  float out_sign;           // +1: out = attention + residual; -1: out = residual - attention (residual construction)
   int dense;                // 1: no index list, every query group attends to all Sk keys (tail of the last tile masked)
   int n_out_peers;          // 0 = not sharded
   int out_rows_per_peer;

@@ -148,9 +148,13 @@ def _extras_checks(residual, perm, q, out_dtype, batch_size, num_head, seqlen_q,
     return residual, perm
 
 
-def _launch(args: "_lib.GatherAttnArgs", device, where: str, out_peers=None) -> None:
+def _launch(args: "_lib.GatherAttnArgs", device, where: str, out_peers=None, subtract: bool = False) -> None:
     stream = torch.cuda.current_stream(device).cuda_stream
-    if out_peers is None:
+    if subtract:
+        if out_peers is not None:
+            raise ValueError("residual_minus_attention and out_peers cannot be combined")
+        rc = _lib.lib().mcs_gather_attn_residual_fwd(args, stream)
+    elif out_peers is None:
         rc = _lib.lib().mcs_gather_attn_fwd(args, stream)
     else:
         import ctypes as C
@@ -199,6 +203,7 @@ def flash_attn_gather_kv_func(
     perm: Optional[torch.Tensor] = None,
     group_rows: int = 128,
     out_peers=None,
+    residual_minus_attention: bool = False,
 ):
     """Forward-only token-level sparse gather-KV attention on B200.
 
@@ -274,7 +279,9 @@ def flash_attn_gather_kv_func(
     if out_peers is not None:
         args.out = None
         args.o_stride[0], args.o_stride[1], args.o_stride[2] = (int(x) for x in out_peers[2])
-    _launch(args, device, "flash_attn_gather_kv_func", out_peers)
+    if residual_minus_attention and residual is None:
+        raise ValueError("residual_minus_attention needs residual (the dense attention output, (B,H,Sq,D))")
+    _launch(args, device, "flash_attn_gather_kv_func", out_peers, subtract=residual_minus_attention)
     return (out, lse) if return_lse else (out, None)
 
 

@@ -281,12 +281,13 @@ class TokenSparseBackend:
     def __init__(self, config: TokenSparseConfig):
         self.config = config
 
-    def _sparse(self, q, k, v, gi, gl, scale, residual, perm):
+    def _sparse(self, q, k, v, gi, gl, scale, residual, perm, subtract: bool = False):
         from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import flash_attn_gather_kv_func
         # (B,H,L,D) storage viewed as (B,L,H,D): no copies, the kernel takes the strides
         out = torch.empty_like(q)
         flash_attn_gather_kv_func(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gi, softmax_scale=scale,
-                                  gather_kv_lengths=gl, out=out.transpose(1, 2), residual=residual, perm=perm)
+                                  gather_kv_lengths=gl, out=out.transpose(1, 2), residual=residual, perm=perm,
+                                  residual_minus_attention=subtract)
         return out
 
     def forward(self, cache: TokenSparseCache, q, k, v, scale: Optional[float] = None):
@@ -313,8 +314,9 @@ class TokenSparseBackend:
             gi, gl = _select_topk_tokens(mass, cfg.topk, tile_n=cfg.tile_n, sink_ranges=cfg.sink_ranges)
             cache._cached_indices, cache._cached_lengths, cache._cached_len = gi, gl, (L, k.shape[2])
             if cfg.bias_correction:
-                sparse_grp = self._sparse(q_grp, k, v, gi, gl, scale, None, None)
-                cache._cached_residual = (dense_grp - sparse_grp).to(q.dtype)    # permuted-query order
+                # residual = dense - sparse in one kernel pass (the reference runs the sparse kernel and then an
+                # elementwise subtraction, token_sparse.py:1209-1216); permuted-query order
+                cache._cached_residual = self._sparse(q_grp, k, v, gi, gl, scale, dense_grp, None, subtract=True)
                 cache._residual_perm_gen = cache._perm_generation
             if perm is None:
                 return dense_grp

@@ -158,3 +158,23 @@ def test_argument_errors(cuda_device):
         flash_attn_func(q, k, v, gi, causal=True)
     with pytest.raises(RuntimeError):
         flash_attn_gather_kv_func(q.requires_grad_(True), k, v, gi)
+
+
+def test_residual_minus_attention(cuda_device):
+    """Residual construction in one pass: out = residual - attention (fp32 subtraction, one rounding)."""
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    from mcsparse_b200 import synth
+    B, H, L, D, KS = 1, 2, 640, 128, 256
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(B, L, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    dense = torch.randn(B, H, L, D, generator=g).to(torch.bfloat16)
+    gi = synth.random_sorted_indices(B, H, L // 128, KS, L, seed=4)
+    sparse, _ = gather_attn_ref(q, k, v, gi)
+    ref = dense.float().permute(0, 2, 1, 3) - sparse
+    out, _ = flash_attn_gather_kv_func(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), gi.to(cuda_device),
+                                       residual=dense.to(cuda_device), residual_minus_attention=True)
+    mx, mr = error_metrics(out.float().cpu(), ref)
+    assert mx < 2e-2 and mr < 1e-2, (mx, mr)
+    with pytest.raises(ValueError):
+        flash_attn_gather_kv_func(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), gi.to(cuda_device),
+                                  residual_minus_attention=True)
