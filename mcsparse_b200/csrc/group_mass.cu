@@ -24,8 +24,9 @@
 // Roles: warps 0-7 exponentiate and sum (two threads per key token: warps w and w+4 share a TMEM
 // lane group and take 64 query columns each, so that every SM sub-partition has two warps feeding
 // its SFU; the two partial sums meet in shared memory), warp 8 issues the MMAs (converged, one
-// elected lane executes the tcgen05 instructions), warps 9-12 stream the key tiles with cp.async
-// into a 3-slot ring.
+// elected lane executes the tcgen05 instructions), warps 9-12 prepare the query operand
+// and stream the key tiles into a 3-slot ring: by TMA (one elected thread, boxes of 128 rows x 128 bytes)
+// when a tensor map can describe K's strides, else with cp.async.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -69,7 +70,9 @@ __device__ __forceinline__ uint32_t swz(int row, int c) {   // 16-byte chunk c o
 }
 
 template <int D, bool kFp16>
-__global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMassParams p) {
+__global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMassParams p, const __grid_constant__ KeyTileMap kmap) {
+  // key tiles are 128 consecutive rows: with a valid tensor map one elected thread loads them by TMA
+  const bool use_tma = kmap.valid != 0;
   using L = Smem<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -90,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
 
   if (tid == 0) {
     for (int i = 0; i < kRing; ++i) {
-      mbar_init(bar(BAR_FULL + i), kProducerThreads);
+      mbar_init(bar(BAR_FULL + i), use_tma ? 1 : kProducerThreads);
       mbar_init(bar(BAR_EMPTY + i), 1);
     }
     mbar_init(bar(BAR_Q_FULL), 2 * kProducerThreads);   // per thread: its cp.async rows + its plain stores
@@ -269,12 +272,37 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
       cp_async_arrive_noinc(bar(BAR_Q_FULL));
     }
     // ---- key tiles: contiguous rows t*128 .. t*128+127 of this head
+    int n_tiles_cp = n_tiles;       // tiles copied with cp.async (none when TMA is used)
     const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + 2 * ((size_t)b * p.k_stride[0] + (size_t)h * p.k_stride[2]) + cch * 16;
     const size_t k_row = 2 * (size_t)p.k_stride[1];
     int slot = 0, phase = 0;
     bool wrapped = false, ok = true;
+    const bool tma_leader = elect_one();
+    if (use_tma) {
+      // one thread of producer warp 0 issues every tile as D / 64 boxes of 128 rows x 128 bytes; rows beyond the
+      // end of the sequence arrive as zeros
+      if (pw == 0) {
+        int co[4] = {0, 0, 0, 0};
+        co[kmap.pos_h] = h;
+        co[kmap.pos_b] = b;
 #pragma unroll 1
-    for (int t = 0; t < n_tiles && ok; ++t) {
+        for (int t = 0; t < n_tiles && ok; ++t) {
+          if (wrapped) ok = mbar_wait(bar(BAR_EMPTY + slot), phase ^ 1, p.status, 44);
+          if (!ok) break;
+          if (tma_leader) {
+            mbar_arrive_expect_tx(bar(BAR_FULL + slot), L::kTileBytes);
+            co[kmap.pos_row] = t * kTile;
+#pragma unroll
+            for (int cb = 0; cb < L::kBlocks; ++cb)
+              tma_load_4d(sRing(slot) + cb * 16384, kmap.k, cb * 64, co[1], co[2], co[3], bar(BAR_FULL + slot));
+          }
+          if (++slot == kRing) { slot = 0; phase ^= 1; wrapped = true; }
+        }
+      }
+      n_tiles_cp = 0;
+    }
+#pragma unroll 1
+    for (int t = 0; t < n_tiles_cp && ok; ++t) {
       if (wrapped) ok = mbar_wait(bar(BAR_EMPTY + slot), phase ^ 1, p.status, 44);
       if (!ok) break;
       const uint32_t dst0 = sRing(slot);
@@ -305,7 +333,9 @@ int launch(const GroupMassParams& p, cudaStream_t stream) {
   auto kern = group_mass_kernel<D, kFp16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return -8;
   const long long grid = (long long)p.B * p.H * p.M;
-  kern<<<(unsigned)grid, kThreads, L::kDynamic, stream>>>(p);
+  KeyTileMap kmap{};
+  kmap.valid = encode_tile_map(p.k, p.k_stride, p.B, p.Lk, p.H, D, kmap.k, kmap.pos_h, kmap.pos_row, kmap.pos_b);
+  kern<<<(unsigned)grid, kThreads, L::kDynamic, stream>>>(p, kmap);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 

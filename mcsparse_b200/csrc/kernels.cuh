@@ -43,6 +43,19 @@ struct alignas(64) DenseTileMaps {
   int valid;     // 0: maps not built, the dense mode gathers rows with cp.async like the sparse mode
 };
 
+// (tensor_map.cu) 4-D tensor map of a (B, S, H, D) tensor of 16-bit elements with element strides {batch, row,
+// head}; box = 64 elements x 128 rows, 128-byte swizzle.  `out` receives the 128-byte map, pos_* the coordinate
+// positions (1..3) of head, row and batch.  False if the layout cannot be described or the driver has no encoder.
+bool encode_tile_map(const void* base, const int64_t* stride, int B, int S, int H, int D, unsigned long long* out,
+                     int& pos_h, int& pos_row, int& pos_b);
+
+// Tensor map of K for the group-mass kernel (see DenseTileMaps)
+struct alignas(64) KeyTileMap {
+  unsigned long long k[16];
+  int pos_h, pos_row, pos_b;
+  int valid;     // 0: key tiles are copied with cp.async
+};
+
 struct GroupMassParams {
   const void* q;        // (B, Lq, H, D) strided
   const void* k;        // (B, Lk, H, D) strided

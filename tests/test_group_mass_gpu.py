@@ -50,3 +50,21 @@ def test_mass_with_perm_and_normalize(cuda_device):
     tp = _compute_token_probs(qp.to(dev), k.to(dev), lse_p.to(dev), 128, 1.0 / D ** 0.5)
     assert tp.dtype == torch.bfloat16 and tuple(tp.shape) == (B, H, 3, L)
     assert (tp.cpu().double() - ref).abs().max() / ref.abs().max() < 1e-2
+
+
+def test_mass_with_keys_shared_by_heads(cuda_device):
+    """K expanded over the heads (head stride 0): no tensor map describes that layout, so the kernel copies the key
+    tiles with cp.async instead of TMA; the result must not depend on the route."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import group_mass
+    B, H, L, D = 1, 2, 600, 128
+    q, k = _clustered(B, H, L, D, 4, torch.bfloat16)
+    k1 = k[:, :1]
+    lse = dense_lse_ref(q, k1.expand(B, H, L, D)).float()
+    ref = group_mass_ref(q, k1.expand(B, H, L, D).contiguous(), lse)
+    dev = cuda_device
+    kd = k1.to(dev).expand(B, H, L, D)
+    assert kd.stride(1) == 0
+    out = group_mass(q.to(dev), kd, lse.to(dev)).cpu().double()
+    assert (out - ref).abs().max() / ref.abs().max() < 2e-3
+    both = group_mass(q.to(dev), kd.contiguous(), lse.to(dev)).cpu().double()      # TMA route, same numbers
+    assert torch.equal(out, both)
