@@ -124,7 +124,9 @@ def run_reference(args):
         return
     import torch
     from mcsparse_b200 import synth
-    shape = synth.C2
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    which = args.shape if args.shape != "auto" else ("c2" if world == 1 else "c5")
+    shape = synth.C2 if which == "c2" else synth.C5          # the workload of the other arm at this GPU count
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     from oracle.gather_attn import gather_attn_ref
@@ -140,7 +142,7 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     ms = dt / args.steps * 1e3
     val = shape.attn_flops(heads_per_step) / (ms * 1e-3) / 1e12
-    sample = f"{heads_per_step} of {shape.heads} heads per step (all 256 groups), torch fp32 on host"
+    sample = f"{heads_per_step} of {shape.heads} heads per step (all {shape.n_groups} groups), torch fp32 on host"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -149,6 +151,37 @@ def run_reference(args):
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def _single_gpu_same_workload(shape, dev, attn_fn, steps: int = 3):
+    """All heads of `shape` on one GPU, in head chunks launched back to back (device-resident, CUDA events)."""
+    import torch
+    from mcsparse_b200 import synth
+    hc = 8 if shape.heads % 8 == 0 else shape.heads
+    parts = []
+    for h0 in range(0, shape.heads, hc):
+        q, k, v = synth.clustered_qkv(shape, heads=hc, head_offset=h0, device=dev)
+        res = synth.residual_like(shape, heads=hc, seed=100 + h0, device=dev)
+        parts.append((q, k, v, res, synth.topmass_indices(q, k, shape), torch.empty_like(q)))
+
+    def run():
+        for q, k, v, res, gi, out in parts:
+            attn_fn(q, k, v, gi, out=out, residual=res)
+
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    del parts
+    torch.cuda.empty_cache()
+    return {"n_gpus": 1, "ms_per_step": ms, "value": shape.attn_flops() / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "steps": steps, "launches_per_step": shape.heads // hc}
 
 
 def run_ours(args):
@@ -169,7 +202,10 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    shape = synth.C2
+    # one GPU: the bf16 video-DiT shape the headline metric is quoted on; several GPUs: the attention of the
+    # Ulysses context-parallel layer (long-video grid, 40 heads), the configuration named for 2/4/8 GPUs
+    which = args.shape if args.shape != "auto" else ("c2" if world == 1 else "c5")
+    shape = synth.C2 if which == "c2" else synth.C5
     if args.heads:
         # reduced head count: a small case of the same kernel for profiler captures, not a bench line
         import dataclasses
@@ -195,11 +231,13 @@ def run_ours(args):
         v_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
         if args.ulysses == "fused":
             # peer-store scatter in front, attention epilogue storing into the owners' sequence shards
-            ul = UlyssesFusedAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
+            dma_from = {"sm": None, "mixed": 1, "dma": 0}[args.scatter]
+            ul = UlyssesFusedAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks, dma_from_chunk=dma_from)
 
             def attn(qh, kh, vh, h0, h1, out_peers):
                 flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], residual=residual[:, h0:h1], out_peers=out_peers)
-            launches_per_step = 4 * ul.chunks            # 3 scatters + 1 attention per head chunk
+            # one attention kernel per head chunk + three scatter kernels per chunk that is not moved by the copy engines
+            launches_per_step = ul.chunks + 3 * (ul.chunks if dma_from is None else min(dma_from, ul.chunks))
         else:
             # library all-to-alls around the attention (comparison arm)
             ul = UlyssesSparseAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks)
@@ -234,6 +272,13 @@ def run_ours(args):
         step()
     barrier()
     _lib.check_status(dev, "bench warm-up")
+
+    # several GPUs: the same workload (all heads) on rank 0's GPU alone, outside the timed region, as the
+    # single-GPU figure of this very shape measured in the same run
+    single = None
+    if world > 1 and rank == 0 and not args.no_single:
+        single = _single_gpu_same_workload(shape, dev, flash_attn_gather_kv_func)
+    barrier()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -318,20 +363,22 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": shape.n_groups,
-                       "topk": shape.topk, "residual": "fused", "indices": "4 sinks + top-2044 by exact fp32 group mass, ascending",
-                       "parallelism": (f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" + ("-graph" if args.graph and args.ulysses == "fused" else "")) if world > 1 else "single",
-                       "l2": "inputs (1.06 GB per call) larger than L2; no explicit flush"},
+                       "topk": shape.topk, "residual": "fused", "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass, ascending",
+                       "parallelism": (f"ulysses{world}-{args.ulysses}-chunks{ul.chunks}" + (f"-scatter_{args.scatter}" if args.ulysses == "fused" else "") + ("-graph" if args.graph and args.ulysses == "fused" else "")) if world > 1 else "single",
+                       "l2": f"inputs ({(4 * q.numel() * 2 + gi.numel() * 4) / 1e9:.2f} GB per call and GPU) larger than L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
                     "d2h_bytes_per_step": out.numel() * out.element_size()},
             "roofline": roofline,
         }
+        if single is not None:
+            line["single_gpu_same_workload"] = single
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cv, heads_done, secs = _cpu_oracle_sample(shape, args.cpu_budget, threads)
             line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"{heads_done} of {H} heads, all 256 groups each, {secs:.1f} s, torch fp32"}
+                                    "sample": f"{heads_done} of {H} heads, all {shape.n_groups} groups each, {secs:.1f} s, torch fp32"}
         print(json.dumps(line))
     if world > 1:
         # Leave without running destructors: symmetric-memory handles, a captured graph that contains
@@ -469,10 +516,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--chunks", type=int, default=1, help="head chunks of the Ulysses pipeline (N > 1)")
+    ap.add_argument("--chunks", type=int, default=2,
+                    help="head chunks of the Ulysses pipeline (N > 1); lowered to a divisor of the local head count")
     ap.add_argument("--graph", action="store_true", help="N > 1, fused: replay one captured CUDA graph per step instead of launching eagerly")
     ap.add_argument("--ulysses", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store reshard fused with the attention kernel, or library all-to-alls around it")
+    ap.add_argument("--scatter", default="mixed", choices=["sm", "mixed", "dma"],
+                    help="N > 1, fused: reshard by the scatter kernel, by the copy engines, or (mixed) kernel for the first "
+                         "head chunk and copy engines for the chunks that move under an attention kernel")
+    ap.add_argument("--shape", default="auto", choices=["auto", "c2", "c5"],
+                    help="attn workload: c2 = L=32,760 H=24 top-k 2048 (default on one GPU); c5 = attention of the Ulysses "
+                         "layer, L=98,280 H=40 top-k 4096 in bf16 (default on several GPUs)")
+    ap.add_argument("--no-single", action="store_true", help="N > 1: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "

@@ -150,6 +150,13 @@ int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers
                         int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream);
 
 /*
+ * The same reshard, same arguments and result, issued as one strided 2-D device copy per peer on the copy
+ * engines instead of a kernel: for head chunks that are exchanged while an attention kernel occupies the SMs.
+ */
+int mcs_ulysses_scatter_dma(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                            int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream);
+
+/*
  * Anchor-step group mass: mass[b,h,m,j] = sum_{i in group m} exp(scale * q_i . k_j - lse_i), fp32.
  *
  * Replaces: mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-117

@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "mcs_dense_attn_fwd",
     "mcs_gather_attn_residual_fwd",
     "mcs_ulysses_scatter",
+    "mcs_ulysses_scatter_dma",
     "mcs_group_mass",
     "mcs_topk_select",
     "mcs_pddp_workspace_bytes",
@@ -116,6 +117,8 @@ def lib() -> C.CDLL:
     L.mcs_ulysses_scatter.restype = C.c_int
     L.mcs_ulysses_scatter.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int64, C.c_int64, C.c_void_p]
+    L.mcs_ulysses_scatter_dma.restype = C.c_int
+    L.mcs_ulysses_scatter_dma.argtypes = L.mcs_ulysses_scatter.argtypes
     L.mcs_set_clock_buffer.restype = None
     L.mcs_set_clock_buffer.argtypes = [C.c_void_p]
     L.mcs_sm_clock_probe.restype = C.c_int

@@ -148,8 +148,8 @@ int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* a, void* const* out_
   return gather_attn_dispatch(a, out_peers, n_peers, rows_per_peer, false, stream);
 }
 
-int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
-                        int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream) {
+static int ulysses_scatter_checked(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                                   int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream, bool dma) {
   if (src == nullptr || dst_peers == nullptr) return MCS_ERR_NULL_POINTER;
   if (n_peers < 1 || n_peers > 16 || rank < 0 || rank >= n_peers || rows < 0 || seg_bytes < 16) return MCS_ERR_BAD_SHAPE;
   if (seg_stride_bytes < seg_bytes || src_row_bytes < seg_stride_bytes * (n_peers - 1) + seg_bytes) return MCS_ERR_BAD_SHAPE;
@@ -158,8 +158,18 @@ int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers
     if (dst_peers[i] == nullptr) return MCS_ERR_NULL_POINTER;
     if (!aligned16(dst_peers[i])) return MCS_ERR_BAD_ALIGNMENT;
   }
-  return mcs::launch_ulysses_scatter(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes,
-                                     static_cast<cudaStream_t>(stream));
+  auto* fn = dma ? mcs::launch_ulysses_scatter_dma : mcs::launch_ulysses_scatter;
+  return fn(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                        int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream) {
+  return ulysses_scatter_checked(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, stream, false);
+}
+
+int mcs_ulysses_scatter_dma(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
+                            int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream) {
+  return ulysses_scatter_checked(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, stream, true);
 }
 
 int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {

@@ -113,6 +113,8 @@ int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t 
 int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
 
 // Sequence-to-head reshard by peer stores (see reshard.cu)
+int launch_ulysses_scatter_dma(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
+                               long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);
 int launch_ulysses_scatter(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
                            long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);
 

@@ -205,16 +205,18 @@ class UlyssesSparseAttention:
 
 
 def ulysses_scatter(src: torch.Tensor, dst_ptrs: Sequence[int], rank: int, rows: int, seg_bytes: int,
-                    seg_stride_bytes: int, src_row_bytes: int) -> None:
-    """Launch ``mcs_ulysses_scatter`` on the current stream: segment r of every local row goes to peer r."""
+                    seg_stride_bytes: int, src_row_bytes: int, dma: bool = False) -> None:
+    """Launch ``mcs_ulysses_scatter`` on the current stream: segment r of every local row goes to peer r.
+    ``dma`` issues the same reshard as strided device copies on the copy engines (``mcs_ulysses_scatter_dma``)."""
     import ctypes as C
     from .. import _lib
     table = (C.c_void_p * len(dst_ptrs))(*[int(x) for x in dst_ptrs])
     stream = torch.cuda.current_stream(src.device).cuda_stream
-    rc = _lib.lib().mcs_ulysses_scatter(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows),
-                                        int(seg_bytes), int(seg_stride_bytes), int(src_row_bytes), C.c_void_p(stream))
+    fn = _lib.lib().mcs_ulysses_scatter_dma if dma else _lib.lib().mcs_ulysses_scatter
+    rc = fn(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows), int(seg_bytes), int(seg_stride_bytes),
+            int(src_row_bytes), C.c_void_p(stream))
     if rc != 0:
-        raise RuntimeError(f"mcs_ulysses_scatter: {_lib.error_string(rc)} (code {rc})")
+        raise RuntimeError(f"mcs_ulysses_scatter{'_dma' if dma else ''}: {_lib.error_string(rc)} (code {rc})")
 
 
 class PeerBuffers:
@@ -274,7 +276,12 @@ class UlyssesFusedAttention:
     """
 
     def __init__(self, group, seq_len: int, heads: int, head_dim: int, dtype, device, chunks: int = 2,
-                 buffers: Optional[PeerBuffers] = None, rank: Optional[int] = None, world: Optional[int] = None):
+                 buffers: Optional[PeerBuffers] = None, rank: Optional[int] = None, world: Optional[int] = None,
+                 dma_from_chunk: Optional[int] = 1):
+        # head chunks from this one on are exchanged by the copy engines: they move while the attention of
+        # an earlier chunk owns the SMs, where a scatter kernel could not become resident.  Chunk 0 has
+        # the GPU to itself and uses the kernel.  None: the kernel for every chunk.
+        self.dma_from_chunk = dma_from_chunk
         self.group = group
         self.world = world if world is not None else dist.get_world_size(group)
         self.rank = rank if rank is not None else dist.get_rank(group)
@@ -306,12 +313,13 @@ class UlyssesFusedAttention:
 
     def scatter_chunk(self, q, k, v, c: int) -> None:
         """Pushes head chunk c of this rank's q, k, v shards to all peers (current stream)."""
+        dma = self.dma_from_chunk is not None and c >= self.dma_from_chunk
         D, hc, Hl, H, es = self.D, self.hc, self.Hl, self.H, self.esize
         seg, seg_stride, row = hc * D * es, Hl * D * es, H * D * es
         plane = self.L * hc * D * es                       # bytes of one of q / k / v inside recv[c]
         for i, t in enumerate((q, k, v)):
             src = t.view(self.Ls, H, D)[:, c * hc:, :]     # chunk c of rank 0's heads; peers follow at seg_stride
-            ulysses_scatter(src, [p + i * plane for p in self.buf.recv_ptrs[c]], self.rank, self.Ls, seg, seg_stride, row)
+            ulysses_scatter(src, [p + i * plane for p in self.buf.recv_ptrs[c]], self.rank, self.Ls, seg, seg_stride, row, dma=dma)
 
     def out_peers(self, c: int):
         """(pointers, rows per peer, strides) for the attention of head chunk c."""

@@ -50,6 +50,8 @@ class VideoShape:
 C2 = VideoShape("dit_L32760_H24_D128_topk2048", 24, (21, 39, 40), (3, 6, 6), topk=2048)
 # FP8 long-video shape: H=40, L=98,280 (21x72x65), top-k 4096 -> 768 groups
 C3 = VideoShape("dit_L98280_H40_D128_topk4096", 40, (21, 72, 65), (7, 12, 11), topk=4096)
+# attention of the Ulysses context-parallel layer: the long-video grid in bf16, 40 heads sharded over the ranks
+C5 = VideoShape("ulysses_dit_L98280_H40_D128_topk4096", 40, (21, 72, 65), (7, 12, 11), topk=4096)
 
 
 def cluster_ids(shape: VideoShape) -> torch.Tensor:
@@ -116,7 +118,7 @@ def topmass_indices(q: torch.Tensor, k: torch.Tensor, shape: VideoShape, heads_p
     """Anchor-step selection with this package's own kernels, as the benchmark configuration defines its
     indices: per query group the 4 sink tokens plus the (topk - 4) tokens of highest exact fp32 group
     mass, ascending int32 (1, H, M, topk).  q, k: (1, L, H, D) CUDA tensors.  The dense log-sum-exp that
-    the mass needs comes from torch's flash attention (an input of the anchor step, not part of it)."""
+    the mass needs comes from the attention kernel's dense mode."""
     from mcsparse_b200.kernels.flash_mcsa.token_sparse import dense_attention_with_lse, group_mass, select_topk_with_sinks
     H, D = q.shape[2], q.shape[3]
     scale = 1.0 / math.sqrt(D)
