@@ -14,9 +14,11 @@ Pinning status (how each restatement is anchored to the reference):
   (interface.py:121-136, flash_fwd_sm90.py:826-829, softmax.py:126-227) and is
   cross-checked against dense torch attention on full index sets
   (``tests/test_oracle.py``).
-* group mass (``group_mass``): restates block_probs.py:27-89 (a Triton kernel that
-  needs a GPU); cross-checked against the softmax identity sum_j tp = 1.  PARITY
-  UNPINNED against reference outputs.
+* group mass (``group_mass``): pinned — restates block_probs.py:27-89 and is compared with
+  outputs of that very Triton kernel, executed on the CPU by Triton's interpreter on
+  seeded fp16 and bf16-valued inputs (``tests/golden/mass_reference.pt``, written by
+  ``tests/golden/make_golden.py``); also cross-checked against the identity
+  sum_j tp = 1.
 * token selection (``select``): pinned — compared on CPU with the reference's own
   ``_select_topk_tokens`` imported from the reference tree when it is present, and
   with committed golden vectors generated from it (``tests/golden``).

@@ -3,8 +3,9 @@
 Restates mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-89: per (head, query block m,
 key j) ``(1/n_m) * sum_{i in block m} exp(scale * q_i . k_j - lse_i)``, rows past L_Q contribute 0
 (:77) and the divisor is the number of real rows in the block (:79-80).  ``normalize=False`` gives
-the plain sum.  Parity against reference outputs is unpinned (the reference kernel needs a GPU and
-ships no vectors); the identity ``sum_j mass = n_m`` for an exact lse is checked instead.
+the plain sum.  Pinned: ``tests/test_oracle.py`` compares it with outputs of the reference kernel
+itself (run through Triton's CPU interpreter by ``tests/golden/make_golden.py``); the identity
+``sum_j mass = n_m`` for an exact lse is checked as well.
 """
 
 from __future__ import annotations

@@ -1,13 +1,22 @@
-"""Generates the golden fixtures in this directory by running the REFERENCE's own CPU-runnable code
-(Fast PDDP and token selection) on small seeded inputs.  Needs the reference tree on sys.path
+"""Generates the golden fixtures in this directory by running the REFERENCE's own code on small seeded
+inputs: Fast PDDP and token selection (plain torch, CPU) and the group-mass kernel
+(``ops/triton/block_probs.py``, a Triton kernel, executed on the CPU by Triton's interpreter,
+``TRITON_INTERPRET=1``).  Needs the reference tree on sys.path
 (``PYTHONPATH=/path/to/mcsparse python tests/golden/make_golden.py``); the fixtures it writes are
 committed, so the tests themselves never need the reference.
 """
 
+import math
+import os
 import sys
 from pathlib import Path
 
+os.environ.setdefault("TRITON_INTERPRET", "1")     # must be set before triton is imported
+
 import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+from mass_cases import MASS_CASES, mass_inputs  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 
@@ -37,6 +46,22 @@ def main():
         sel.append({"L": L, "ratio": ratio, "sinks": sinks, "seed": seed, "gi": gi, "gl": gl})
     torch.save(sel, HERE / "select_reference.pt")
     print("wrote", HERE / "pddp_reference.pt", HERE / "select_reference.pt")
+    mass_golden()
+
+
+def mass_golden():
+    """Group mass by the reference's own Triton kernel (block_probs.py:27-117: mean over the block's rows,
+    output in the input dtype)."""
+    from mcsparse.kernels.flash_mcsa.ops.triton.block_probs import _compute_token_probs_bf16_triton
+    out = []
+    for case in MASS_CASES:
+        q, k, lse, scale = mass_inputs(case)
+        M = math.ceil(case["Lq"] / 128)
+        tp = _compute_token_probs_bf16_triton(q, k, lse, 128, M, scale)
+        assert torch.isfinite(tp.float()).all()
+        out.append({**case, "token_probs": tp})
+    torch.save(out, HERE / "mass_reference.pt")
+    print("wrote", HERE / "mass_reference.pt")
 
 
 if __name__ == "__main__":

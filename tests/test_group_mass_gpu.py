@@ -68,3 +68,32 @@ def test_mass_with_keys_shared_by_heads(cuda_device):
     assert (out - ref).abs().max() / ref.abs().max() < 2e-3
     both = group_mass(q.to(dev), kd.contiguous(), lse.to(dev)).cpu().double()      # TMA route, same numbers
     assert torch.equal(out, both)
+
+
+def test_mass_matches_reference_kernel_output(cuda_device):
+    """The CUDA kernel against outputs of the reference's own Triton kernel (block_probs.py:27-117) on the same
+    seeded inputs; the fixtures were produced by tests/golden/make_golden.py with Triton's CPU interpreter.
+    fp16 cases run the kernel on the very same fp16 tensors; the "bf16_as_f32" cases carry bf16 values in fp32
+    (exact products), so the kernel runs on their bf16 form."""
+    import sys
+    from pathlib import Path
+    golden = Path(__file__).resolve().parent / "golden"
+    sys.path.insert(0, str(golden))
+    from mass_cases import mass_inputs
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import _compute_token_probs, group_mass
+    dev = cuda_device
+    for c in torch.load(golden / "mass_reference.pt"):
+        q, k, lse, scale = mass_inputs(c)
+        if c["dtype"] == "bf16_as_f32":
+            q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)       # exact: the values are bf16 already
+        ref = c["token_probs"].double()
+        mean = group_mass(q.to(dev), k.to(dev), lse.to(dev), scale=scale, normalize=True).cpu().double()
+        assert (mean - ref).abs().max() / ref.abs().max() < 2e-3, c
+        # fp32 sum (what the selection ranks on) = the reference's mean times the rows of the block
+        rows = torch.tensor([min(128, c["Lq"] - 128 * m) for m in range(ref.shape[2])], dtype=torch.float64)
+        total = group_mass(q.to(dev), k.to(dev), lse.to(dev), scale=scale).cpu().double()
+        assert (total - ref * rows.view(1, 1, -1, 1)).abs().max() / (ref * rows.view(1, 1, -1, 1)).abs().max() < 2e-3
+        # reference-shaped wrapper: mean rounded to the input dtype, as the reference stores it
+        tp = _compute_token_probs(q.to(dev), k.to(dev), lse.to(dev), 128, scale)
+        assert tp.dtype == q.dtype
+        assert (tp.cpu().double() - ref).abs().max() / ref.abs().max() < (1e-2 if q.dtype == torch.bfloat16 else 3e-3)
