@@ -33,6 +33,9 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "gather_kv_sparse_attn_effective_tflops"
 UNIT = "TFLOP/s"
+# DRAM traffic of one attention-kernel launch per head, from ncu captures of 4-head launches
+# (dram__bytes_read.sum + dram__bytes_write.sum; summaries under profiles/)
+NCU_DRAM_BYTES_PER_HEAD = {"c2": 0.94e9 / 24}
 
 
 def _peaks():
@@ -97,6 +100,48 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _config(shape, world: int, args, q_bytes_per_gpu: float):
+    """The ``config`` object of the JSON line; both arms build it from the same arguments."""
+    if world > 1:
+        par = f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" + (f"-scatter_{args.scatter}" if args.ulysses == "fused" else "") + \
+              ("-graph" if args.graph and args.ulysses == "fused" else "")
+    else:
+        par = "single"
+    return {"workload": shape.name, "B": 1, "H": shape.heads, "L": shape.seq_len, "D": shape.head_dim, "groups": shape.n_groups,
+            "topk": shape.topk, "residual": "fused",
+            "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass, ascending", "parallelism": par,
+            "l2": f"inputs ({q_bytes_per_gpu / 1e9:.2f} GB per call and GPU) larger than L2; no explicit flush"}
+
+
+def _input_bytes_per_gpu(shape, world: int) -> float:
+    hl = shape.heads // world
+    return 4.0 * shape.seq_len * hl * shape.head_dim * 2 + hl * shape.n_groups * shape.topk * 4.0
+
+
+def _cpu_topmass_indices(q, k, shape, rows_per_chunk: int = 2048):
+    """The configuration's index definition evaluated on the host for one head (oracle arithmetic, fp32,
+    query groups a few at a time): 4 sinks + the top tokens by group mass, ascending."""
+    import math
+    import torch
+    from oracle.select import select_topk_ref
+    L, D = shape.seq_len, shape.head_dim
+    qf, kf = q[0, :, 0].float(), k[0, :, 0].float()
+    scale = 1.0 / math.sqrt(D)
+    mass = torch.empty(shape.n_groups, L)
+    for r0 in range(0, L, rows_per_chunk):
+        r1 = min(L, r0 + rows_per_chunk)
+        s = (qf[r0:r1] @ kf.T) * scale
+        pr = torch.exp(s - torch.logsumexp(s, -1, keepdim=True))
+        for g0 in range(r0, r1, shape.group_rows):
+            mass[g0 // shape.group_rows] = pr[g0 - r0:min(g0 - r0 + shape.group_rows, r1 - r0)].sum(0)
+    return select_topk_ref(mass, shape.topk, range(synth_n_sink())).view(1, 1, shape.n_groups, shape.topk)
+
+
+def synth_n_sink() -> int:
+    from mcsparse_b200 import synth
+    return synth.N_SINK
+
+
 def _cpu_oracle_sample(shape, budget_s: float, threads: int):
     """Times the CPU oracle (port of the reference math) on whole heads of the workload until
     ``budget_s`` is used.  Returns (tflops, heads_done, seconds)."""
@@ -107,7 +152,7 @@ def _cpu_oracle_sample(shape, budget_s: float, threads: int):
     done, elapsed = 0, 0.0
     while done < shape.heads and (done == 0 or elapsed < budget_s):
         q, k, v = synth.clustered_qkv(shape, heads=1, head_offset=done)
-        res = synth.residual_like(shape, heads=1, seed=1 + done)
+        res = synth.residual_like(shape, heads=1, head_offset=done)
         gi = synth.random_sorted_indices(1, 1, shape.n_groups, shape.topk, shape.seq_len, seed=done)
         t0 = time.perf_counter()
         gather_attn_ref(q, k, v, gi, residual=res)
@@ -133,7 +178,7 @@ def run_reference(args):
     heads_per_step = 1
     q, k, v = synth.clustered_qkv(shape, heads=heads_per_step)
     res = synth.residual_like(shape, heads=heads_per_step)
-    gi = synth.random_sorted_indices(1, heads_per_step, shape.n_groups, shape.topk, shape.seq_len)
+    gi = _cpu_topmass_indices(q, k, shape)          # same index definition as the other arm, built outside the timed steps
     for _ in range(args.warmup):
         gather_attn_ref(q, k, v, gi, residual=res)
     t0 = time.perf_counter()
@@ -147,21 +192,61 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": shape.name, "sample": sample},
+        "config": _config(shape, world, args, _input_bytes_per_gpu(shape, world)),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def _single_gpu_same_workload(shape, dev, attn_fn, steps: int = 3):
-    """All heads of `shape` on one GPU, in head chunks launched back to back (device-resident, CUDA events)."""
+def _oracle_check(q, k, v, gi, residual, out, head: int, fp8=None):
+    """Compares one head of a finished attention call with the CPU oracle (outside any timed region).
+    q, k, v, out: (1, L, H, D) device tensors, residual (1, H, L, D), gi (1, H, M, K).  Returns the error figures
+    and whether they are inside the tolerance stated for the path."""
+    import torch
+    from oracle.gather_attn import error_metrics, gather_attn_fp8_ref, gather_attn_ref
+    sl = slice(head, head + 1)
+    c = lambda t: t.cpu()
+    if fp8 is None:
+        ref, _ = gather_attn_ref(c(q[:, :, sl]), c(k[:, :, sl]), c(v[:, :, sl]), c(gi[:, sl]), residual=c(residual[:, sl]))
+        tol = (2e-2, 1e-2)
+    else:
+        scale_qk, scale_v = fp8
+        ref, _ = gather_attn_fp8_ref(c(q[:, :, sl]), c(k[:, :, sl]), c(v[:, :, sl]), c(gi[:, sl]), c(scale_qk[:, sl]),
+                                     c(scale_v[:, sl]), residual=c(residual[:, sl]))
+        tol = (6e-2, 3e-2)
+    mx, mr = error_metrics(c(out[:, :, sl]).float(), ref)
+    return {"against": "cpu oracle, fp32", "head": head, "max_abs": mx, "mean_rel": mr, "tol_max_abs": tol[0],
+            "tol_mean_rel": tol[1], "ok": bool(mx < tol[0] and mr < tol[1])}
+
+
+def _sequence_shards(shape, rank: int, world: int, dev, hc: int = 8):
+    """This rank's (1, L/N, H, D) sequence shards of the SAME clustered q, k, v whose head shards the indices
+    are built from (heads generated a few at a time to bound memory)."""
+    import torch
+    from mcsparse_b200 import synth
+    H, L, D = shape.heads, shape.seq_len, shape.head_dim
+    Ls = L // world
+    outs = [torch.empty(1, Ls, H, D, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+    for h0 in range(0, H, hc):
+        n = min(hc, H - h0)
+        full = synth.clustered_qkv(shape, heads=n, head_offset=h0, device=dev)
+        for o, t in zip(outs, full):
+            o[:, :, h0:h0 + n] = t[:, rank * Ls:(rank + 1) * Ls]
+        del full
+    return outs
+
+
+def _single_gpu_same_workload(shape, dev, attn_fn, steps: int = 3, compare_rows=None, compare_to=None):
+    """All heads of `shape` on one GPU, in head chunks launched back to back (device-resident, CUDA events).
+    With ``compare_to`` (a (1, rows, H, D) sequence shard produced by the multi-GPU step) the single-GPU outputs
+    of rows ``compare_rows`` are compared with it, and head 0 is compared with the CPU oracle."""
     import torch
     from mcsparse_b200 import synth
     hc = 8 if shape.heads % 8 == 0 else shape.heads
     parts = []
     for h0 in range(0, shape.heads, hc):
         q, k, v = synth.clustered_qkv(shape, heads=hc, head_offset=h0, device=dev)
-        res = synth.residual_like(shape, heads=hc, seed=100 + h0, device=dev)
+        res = synth.residual_like(shape, heads=hc, head_offset=h0, device=dev)
         parts.append((q, k, v, res, synth.topmass_indices(q, k, shape), torch.empty_like(q)))
 
     def run():
@@ -178,10 +263,22 @@ def _single_gpu_same_workload(shape, dev, attn_fn, steps: int = 3):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
+    res = {"n_gpus": 1, "ms_per_step": ms, "value": shape.attn_flops() / (ms * 1e-3) / 1e12, "unit": UNIT,
+           "steps": steps, "launches_per_step": shape.heads // hc}
+    check = None
+    if compare_to is not None:
+        r0, r1 = compare_rows
+        diff = 0.0
+        for i, (q, k, v, r, gi, out) in enumerate(parts):
+            d = (out[:, r0:r1].float() - compare_to[:, :, i * hc:(i + 1) * hc].float()).abs().max()
+            diff = max(diff, float(d))
+        q, k, v, r, gi, out = parts[0]
+        check = _oracle_check(q, k, v, gi, r, out, head=0)
+        check["multi_gpu_shard_vs_single_gpu_max_abs"] = diff
+        check["ok"] = bool(check["ok"] and diff == 0.0)
     del parts
     torch.cuda.empty_cache()
-    return {"n_gpus": 1, "ms_per_step": ms, "value": shape.attn_flops() / (ms * 1e-3) / 1e12, "unit": UNIT,
-            "steps": steps, "launches_per_step": shape.heads // hc}
+    return res, check
 
 
 def run_ours(args):
@@ -216,7 +313,7 @@ def run_ours(args):
     Hl = H // world
     # head shard of this rank (what the attention kernel sees after the all-to-all)
     q, k, v = synth.clustered_qkv(shape, heads=Hl, head_offset=rank * Hl, device=dev)
-    residual = synth.residual_like(shape, heads=Hl, seed=1 + rank, device=dev)
+    residual = synth.residual_like(shape, heads=Hl, head_offset=rank * Hl, device=dev)
     # indices as the configuration defines them: 4 sinks + top-(topk-4) tokens by exact fp32 group mass,
     # built once with this package's own anchor-step kernels (group mass + top-k), outside the timed region
     gi = synth.topmass_indices(q, k, shape)
@@ -226,9 +323,8 @@ def run_ours(args):
     if world > 1:
         from mcsparse_b200.h3.context_parallel import UlyssesFusedAttention, UlyssesSparseAttention
         Ls = L // world
-        q_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
-        k_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
-        v_s = torch.randn(1, Ls, H, D, device=dev, dtype=torch.bfloat16)
+        # sequence shards of the very tensors the indices were built from
+        q_s, k_s, v_s = _sequence_shards(shape, rank, world, dev)
         if args.ulysses == "fused":
             # peer-store scatter in front, attention epilogue storing into the owners' sequence shards
             dma_from = {"sm": None, "mixed": 1, "dma": 0}[args.scatter]
@@ -249,14 +345,16 @@ def run_ours(args):
                 return o
             launches_per_step = ul.chunks
 
+        def eager_step():
+            return ul.forward(q_s, k_s, v_s, attn)
+
         if args.ulysses == "fused" and args.graph:
             graph, _ = ul.capture(q_s, k_s, v_s, attn)
 
             def step():
                 graph.replay()
         else:
-            def step():
-                return ul.forward(q_s, k_s, v_s, attn)
+            step = eager_step
     else:
         def step():
             flash_attn_gather_kv_func(q, k, v, gi, out=out, residual=residual)
@@ -273,11 +371,20 @@ def run_ours(args):
     barrier()
     _lib.check_status(dev, "bench warm-up")
 
-    # several GPUs: the same workload (all heads) on rank 0's GPU alone, outside the timed region, as the
-    # single-GPU figure of this very shape measured in the same run
-    single = None
-    if world > 1 and rank == 0 and not args.no_single:
-        single = _single_gpu_same_workload(shape, dev, flash_attn_gather_kv_func)
+    # ---- correctness of what is being timed, outside the timed region
+    check, single = None, None
+    if world == 1:
+        if not args.no_check:
+            check = _oracle_check(q, k, v, gi, residual, out, head=0)
+    else:
+        shard_out = eager_step().clone()          # this rank's (1, L/N, H, D) output shard of one full step
+        barrier()
+        # the same workload (all heads) on rank 0's GPU alone: the single-GPU time of this very shape measured in the
+        # same run, and the reference the multi-GPU result is compared with (same kernels, same inputs: bit-equal)
+        if rank == 0 and not args.no_single:
+            single, check = _single_gpu_same_workload(shape, dev, flash_attn_gather_kv_func, compare_rows=(0, Ls),
+                                                      compare_to=None if args.no_check else shard_out)
+        del shard_out
     barrier()
 
     sampler = ClockSampler(local_rank)
@@ -315,19 +422,65 @@ def run_ours(args):
 
     # ---- end to end through the public entry point with host buffers
     e2e_steps = max(2, min(args.steps, 5))
-    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
-    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if world == 1:
+        # Host tensors in (B, H, L, D) storage (the entry point takes them as strided (B, L, H, D) views), so that
+        # a head chunk is one contiguous block.  Three streams: inbound copies of chunk c+1, the kernel on chunk c
+        # and the outbound copy of chunk c-1 overlap, one async copy per chunk and tensor; PCIe runs both
+        # directions at once and the step is bounded by the inbound bytes.
+        hcn = args.e2e_chunk if H % args.e2e_chunk == 0 else H
+        hq, hk, hv = (t.permute(0, 2, 1, 3).contiguous().cpu().pin_memory() for t in (q, k, v))
+        hout = torch.empty(1, H, L, D, dtype=out.dtype).pin_memory()
+        dq, dk, dv, do = (torch.empty(1, H, L, D, dtype=q.dtype, device=dev) for _ in range(4))
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        n_ch = H // hcn
+        e2e_launches = n_ch
 
-    def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        if world > 1:
-            o, _ = flash_attn_gather_kv_func(dq, dk, dv, gi, residual=residual)
-        else:
-            o, _ = flash_attn_gather_kv_func(dq, dk, dv, gi, out=out, residual=residual)
-        hout.copy_(o, non_blocking=True)
+        def e2e_step():
+            main = torch.cuda.current_stream()
+            start = torch.cuda.Event()
+            start.record(main)
+            s_in.wait_event(start)            # the previous step's kernels have read dq/dk/dv
+            s_out.wait_event(start)
+            ev_in = [torch.cuda.Event() for _ in range(n_ch)]
+            ev_k = [torch.cuda.Event() for _ in range(n_ch)]
+            with torch.cuda.stream(s_in):
+                for c in range(n_ch):
+                    sl = slice(c * hcn, (c + 1) * hcn)
+                    dq[:, sl].copy_(hq[:, sl], non_blocking=True)
+                    dk[:, sl].copy_(hk[:, sl], non_blocking=True)
+                    dv[:, sl].copy_(hv[:, sl], non_blocking=True)
+                    ev_in[c].record(s_in)
+            for c in range(n_ch):
+                sl = slice(c * hcn, (c + 1) * hcn)
+                main.wait_event(ev_in[c])
+                flash_attn_gather_kv_func(dq[:, sl].transpose(1, 2), dk[:, sl].transpose(1, 2), dv[:, sl].transpose(1, 2),
+                                          gi[:, sl], out=do[:, sl].transpose(1, 2), residual=residual[:, sl])
+                ev_k[c].record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_k[c])
+                    hout[:, sl].copy_(do[:, sl], non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(s_out)
+            main.wait_event(done)
+        h2d = 3 * q.numel() * q.element_size()
+        d2h = out.numel() * out.element_size()
+        e2e_desc = f"pinned host q,k,v in / out, {n_ch} head chunks of {hcn}, inbound copies, kernel and outbound copy on three streams"
+    else:
+        # host sequence shard -> device -> scatter to the peers -> attention -> rows stored into the owners' shards
+        # -> host: the exchange in both directions is inside the step
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q_s, k_s, v_s))
+        hout = torch.empty(1, Ls, H, D, dtype=torch.bfloat16).pin_memory()
+        e2e_launches = launches_per_step
+
+        def e2e_step():
+            q_s.copy_(hq, non_blocking=True)
+            k_s.copy_(hk, non_blocking=True)
+            v_s.copy_(hv, non_blocking=True)
+            o = eager_step()
+            hout.copy_(o, non_blocking=True)
+        h2d = 3 * q_s.numel() * q_s.element_size()
+        d2h = hout.numel() * hout.element_size()
+        e2e_desc = "pinned host sequence shards in, Ulysses step (exchange both ways inside), output shard to pinned host"
 
     e2e_step()
     barrier()
@@ -338,6 +491,10 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    e2e_check = None
+    if world == 1 and not args.no_check:
+        # the bytes that came back to the host are the bytes of the device-resident call
+        e2e_check = bool(torch.equal(hout.permute(0, 2, 1, 3), out.cpu()))
 
     t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -348,13 +505,19 @@ def run_ours(args):
     value = flops / (ms_per_step * 1e-3) / 1e12
     e2e_value = flops / (e2e_ms * 1e-3) / 1e12
 
+    rc = 0
     if rank == 0:
         peaks = _peaks()
         kern_ms = statistics.mean(per) if world == 1 else None
         # dominant kernel: the attention kernel; algorithmic FLOPs per launch = this rank's heads
         achieved = shape.attn_flops(Hl) / ((kern_ms if kern_ms else ms_per_step) * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                    "frac": achieved / peaks["bf16_tflops"],
+                    # DRAM bytes per launch from an ncu capture of a 4-head launch of this kernel and workload
+                    # (dram__bytes_read.sum + dram__bytes_write.sum), scaled by heads: traffic grows with the heads
+                    "traffic": NCU_DRAM_BYTES_PER_HEAD.get(which, 0) * Hl or None,
+                    "traffic_source": "ncu, 4-head capture scaled by heads (profiles/)",
+                    "algorithmic_bytes_per_launch": 5 * q.numel() * 2 + gi.numel() * 4,
                     "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                     "kernel": "gather_attn_kernel<128,bf16>",
                     "algorithmic_flops_per_launch": shape.attn_flops(Hl)}
@@ -362,24 +525,33 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": shape.n_groups,
-                       "topk": shape.topk, "residual": "fused", "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass, ascending",
-                       "parallelism": (f"ulysses{world}-{args.ulysses}-chunks{ul.chunks}" + (f"-scatter_{args.scatter}" if args.ulysses == "fused" else "") + ("-graph" if args.graph and args.ulysses == "fused" else "")) if world > 1 else "single",
-                       "l2": f"inputs ({(4 * q.numel() * 2 + gi.numel() * 4) / 1e9:.2f} GB per call and GPU) larger than L2; no explicit flush"},
+            "config": _config(shape, world, args, _input_bytes_per_gpu(shape, world)),
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
-            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
-                    "d2h_bytes_per_step": out.numel() * out.element_size()},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps, "gpu_launches_per_step": e2e_launches, "how": e2e_desc},
             "roofline": roofline,
         }
+        if e2e_check is not None:
+            line["e2e"]["host_output_equals_device_output"] = e2e_check
+        if check is not None:
+            line["check"] = check
+            if not check["ok"] or e2e_check is False:
+                rc = 3
         if single is not None:
             line["single_gpu_same_workload"] = single
+            sp = single["ms_per_step"] / ms_per_step
+            line["scaling_same_workload"] = {"workload": shape.name, "single_ms": single["ms_per_step"], "multi_ms": ms_per_step,
+                                             "speedup": sp, "efficiency": sp / world,
+                                             "note": "the one-GPU line of this bench is quoted on another workload; this is "
+                                                     "the same workload on one GPU of this box, measured in this run"}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cv, heads_done, secs = _cpu_oracle_sample(shape, args.cpu_budget, threads)
             line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"{heads_done} of {H} heads, all {shape.n_groups} groups each, {secs:.1f} s, torch fp32"}
         print(json.dumps(line))
+        if rc:
+            print("bench.py: the result check failed (see \"check\" in the line above)", file=sys.stderr)
     if world > 1:
         # Leave without running destructors: symmetric-memory handles, a captured graph that contains
         # collectives and the communicators have no defined teardown order between them, and a rank that
@@ -389,7 +561,9 @@ def run_ours(args):
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        os._exit(0)
+        os._exit(rc)
+    if rc:
+        sys.exit(rc)
 
 
 def run_anchor(args):
@@ -459,9 +633,44 @@ def run_anchor(args):
                       "peak_source": peaks["source"]}))
 
 
+def _fp8_dense_peak(dev, n: int = 8192, reps: int = 10, sustain_s: float = 2.0):
+    """Dense e4m3 GEMM rate of this GPU through the library (torch._scaled_mm, n^3, fp32 scales, bf16 out): best of
+    ``reps`` single launches (burst) and back-to-back launches for ``sustain_s`` seconds (sustained).  The
+    denominator of the FP8 roofline; measured live because no stored figure exists for this pool."""
+    import torch
+    a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()            # column-major second operand
+    one = torch.ones((), device=dev)
+    f = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    for _ in range(3):
+        f()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        f()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    flops = 2.0 * n ** 3
+    # sustained: as many launches as fit the time budget by the burst rate
+    iters = max(10, int(sustain_s * 1e3 / best))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        f()
+    e1.record()
+    torch.cuda.synchronize()
+    sus = e0.elapsed_time(e1) / iters
+    return {"fp8_tflops": flops / best / 1e9, "fp8_tflops_sustained": flops / sus / 1e9,
+            "how": f"torch._scaled_mm e4m3 {n}^3, bf16 out: best of {reps} (burst), {iters} launches back to back (sustained)"}
+
+
 def run_fp8(args):
-    """Secondary measurement: the FP8 (e4m3) variant of the attention kernel at the long-video shape
-    (H=40, L=98,280, top-k 4096), device-resident inputs, CUDA events; random ascending indices with sinks."""
+    """The FP8 (e4m3) variant of the attention kernel at the long-video shape (H=40, L=98,280, 768 groups x top-k
+    4096, per-head scales amax/448, bf16 residual and output): device-resident timing, roofline against a
+    dense e4m3 GEMM rate measured in the same run, result check on one head, CPU baseline, end-to-end step."""
     import math
     import torch
     from mcsparse_b200 import _lib, synth
@@ -474,38 +683,104 @@ def run_fp8(args):
         import dataclasses
         shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
     H, L, D = shape.heads, shape.seq_len, shape.head_dim
-    g = torch.Generator(device=dev).manual_seed(7)
-    mk = lambda: torch.randn(1, L, H, D, device=dev, generator=g, dtype=torch.bfloat16)
-    q8, sq = synth.quantize_e4m3_per_head(mk())
-    k8, sk = synth.quantize_e4m3_per_head(mk())
-    v8, sv = synth.quantize_e4m3_per_head(mk())
     M = shape.n_groups
+    # clustered bf16 tensors -> top-mass indices (bf16 anchor-step kernels) -> per-head e4m3 quantisation
+    hc = 8 if H % 8 == 0 else H
+    q8 = torch.empty(1, L, H, D, dtype=torch.float8_e4m3fn, device=dev)
+    k8, v8 = torch.empty_like(q8), torch.empty_like(q8)
+    sq, sk, sv = (torch.empty(1, H, dtype=torch.float32, device=dev) for _ in range(3))
+    gi = torch.empty(1, H, M, shape.topk, dtype=torch.int32, device=dev)
+    for h0 in range(0, H, hc):
+        q, k, v = synth.clustered_qkv(shape, heads=hc, head_offset=h0, device=dev)
+        gi[:, h0:h0 + hc] = synth.topmass_indices(q, k, shape)
+        for dst, sc, t in ((q8, sq, q), (k8, sk, k), (v8, sv, v)):
+            t8, s_ = synth.quantize_e4m3_per_head(t)
+            dst[:, :, h0:h0 + hc] = t8
+            sc[:, h0:h0 + hc] = s_
+        del q, k, v
     scale_qk = (sq * sk * (D ** -0.5) * math.log2(math.e)).view(1, H, 1).expand(1, H, M).contiguous().float()
-    # (random_sorted_indices draws per head to bound its temporary: 768 groups x 98,280 scores each)
-    residual = (0.05 * torch.randn(1, H, L, D, device=dev, generator=g)).to(torch.bfloat16)
-    gi = torch.cat([synth.random_sorted_indices(1, 1, M, shape.topk, L, seed=h, device=dev) for h in range(H)], dim=1)
+    residual = synth.residual_like(shape, heads=H, device=dev)
     out = torch.empty(1, L, H, D, device=dev, dtype=torch.bfloat16)
-    step = lambda: flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, scale_qk, sv.float(), out=out, residual=residual)
+    step = lambda: flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, scale_qk, sv, out=out, residual=residual)
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     _lib.check_status(dev, "fp8 warm-up")
+    check = None if args.no_check else _oracle_check(q8, k8, v8, gi, residual, out, head=0, fp8=(scale_qk, sv))
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.2)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop()
     _lib.check_status(dev, "fp8 timed region")
     ms = e0.elapsed_time(e1) / args.steps
     flops = 4.0 * L * shape.topk * D * H
-    print(json.dumps({
-        "metric": "gather_kv_sparse_attn_fp8_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+    # end to end: e4m3 q, k, v from pinned host memory, bf16 output back to the host, every step
+    hq, hk, hv = (t.view(torch.uint8).cpu().pin_memory() for t in (q8, k8, v8))
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    dq, dk, dv = (torch.empty_like(q8) for _ in range(3))
+
+    def e2e_step():
+        dq.view(torch.uint8).copy_(hq, non_blocking=True)
+        dk.view(torch.uint8).copy_(hk, non_blocking=True)
+        dv.view(torch.uint8).copy_(hv, non_blocking=True)
+        flash_attn_gather_kv_fp8_func(dq, dk, dv, gi, scale_qk, sv, out=out, residual=residual)
+        hout.copy_(out, non_blocking=True)
+    e2e_step()
+    torch.cuda.synchronize()
+    n_e2e = max(2, min(args.steps, 3))
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    peak = _fp8_dense_peak(dev)
+    bf16 = _peaks()
+    achieved = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "gather_kv_sparse_attn_fp8_effective_tflops", "value": achieved, "unit": "TFLOP/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "dtype": "e4m3", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
         "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": M, "topk": shape.topk,
-                   "residual": "fused", "indices": "4 sinks + uniform sample, ascending"},
-        "gpu_launches": args.steps}))
+                   "residual": "fused", "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass (bf16 anchor pass), ascending",
+                   "quantisation": "per head, scale = amax / 448",
+                   "l2": f"inputs ({(3 * q8.numel() + 2 * out.numel() * 2 + gi.numel() * 4) / 1e9:.2f} GB per call) larger than L2; no explicit flush"},
+        "clocks": clocks, "gpu_launches": args.steps,
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 3 * q8.numel(), "d2h_bytes_per_step": out.numel() * 2},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak["fp8_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peak["fp8_tflops"], "frac_of_sustained": achieved / peak["fp8_tflops_sustained"],
+                     "frac_of_2x_bf16_burst": achieved / (2 * bf16["bf16_tflops"]), "traffic": None,
+                     "peak_source": "measured in this run: " + peak["how"], "peak_sustained": peak["fp8_tflops_sustained"],
+                     "kernel": "gather_attn_kernel<128,e4m3>", "algorithmic_flops_per_launch": flops,
+                     "algorithmic_bytes_per_launch": 3 * q8.numel() + 2 * out.numel() * 2 + gi.numel() * 4},
+    }
+    if check is not None:
+        line["check"] = check
+    if not args.no_cpu_baseline:
+        from oracle.gather_attn import gather_attn_fp8_ref
+        threads = os.cpu_count() or 1
+        torch.set_num_threads(threads)
+        c = lambda t: t.cpu()
+        a = (c(q8[:, :, :1]), c(k8[:, :, :1]), c(v8[:, :, :1]), c(gi[:, :1]), c(scale_qk[:, :1]), c(sv[:, :1]))
+        r = c(residual[:, :1])
+        t0 = time.perf_counter()
+        n = 0
+        while n == 0 or time.perf_counter() - t0 < args.cpu_budget:
+            gather_attn_fp8_ref(*a, residual=r)
+            n += 1
+        secs = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 4.0 * L * shape.topk * D * n / secs / 1e12, "unit": "TFLOP/s", "cores": threads,
+                                "kind": "port", "sample": f"head 0 of {H}, all {M} groups, {n} passes, {secs:.1f} s, torch fp32 on dequantised inputs"}
+    print(json.dumps(line))
+    if check is not None and not check["ok"]:
+        sys.exit(3)
 
 
 def main():
@@ -529,6 +804,8 @@ def main():
                          "layer, L=98,280 H=40 top-k 4096 in bf16 (default on several GPUs)")
     ap.add_argument("--no-single", action="store_true", help="N > 1: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
+    ap.add_argument("--e2e-chunk", type=int, default=4, help="heads per chunk of the pipelined end-to-end step (one GPU)")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
                          "attn_fp8: the e4m3 variant at the long-video shape (1 GPU)")

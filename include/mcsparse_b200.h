@@ -95,7 +95,14 @@ typedef struct mcs_gather_attn_args {
   int32_t group_rows;   /* query rows per group, 1..128 (reference: 128) */
   int32_t dtype;        /* MCS_DTYPE_* */
   float softmax_scale;  /* > 0; ignored for e4m3 (scale_qk_log2 carries it) */
+  int32_t flags;        /* MCS_ATTN_* bits, 0 for the behaviour described above */
 } mcs_gather_attn_args;
+
+/* With perm != NULL: read the query rows through the permutation but keep out and lse in the permuted
+ * (group) order, row' = row.  The anchor step wants exactly that: the dense output and LSE of the
+ * regrouped queries without a gathered copy of Q (mcsparse/kernels/flash_mcsa/token_sparse.py:1057-1058
+ * makes that copy before the dense pass at :1151). */
+#define MCS_ATTN_OUT_GROUP_ORDER 1
 
 int mcs_gather_attn_fwd(const mcs_gather_attn_args* args, void* stream);
 

@@ -16,6 +16,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmcsparse_b200.so"
 MCS_DTYPE_BF16 = 0
 MCS_DTYPE_FP16 = 1
 MCS_DTYPE_E4M3 = 2
+MCS_ATTN_OUT_GROUP_ORDER = 1
 # argument-error codes of include/mcsparse_b200.h
 MCS_ERR_NULL_POINTER, MCS_ERR_BAD_SHAPE, MCS_ERR_BAD_HEAD_DIM, MCS_ERR_BAD_DTYPE, MCS_ERR_BAD_ALIGNMENT = -1, -2, -3, -4, -5
 
@@ -58,7 +59,7 @@ class GatherAttnArgs(C.Structure):
         ("o_stride", C.c_int64 * 3), ("r_stride", C.c_int64 * 3),
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
         ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
-        ("softmax_scale", C.c_float),
+        ("softmax_scale", C.c_float), ("flags", C.c_int32),
     ]
 
 
@@ -153,14 +154,26 @@ def launch(fn_name: str, args, device, where: str) -> None:
     import torch
     stream = torch.cuda.current_stream(device).cuda_stream
     rc = getattr(lib(), fn_name)(args, stream)
-    if rc != 0:
-        raise RuntimeError(f"{where}: {error_string(rc)} (code {rc})")
+    raise_on_error(rc, where)
     if check_enabled():
         check_status(device, where)
 
 
 def error_string(code: int) -> str:
     return lib().mcs_error_string(int(code)).decode()
+
+
+class KernelLaunchError(RuntimeError):
+    """An entry point of the C ABI returned a negative code (rejected arguments or a failed launch)."""
+
+    def __init__(self, code: int, where: str):
+        super().__init__(f"{where}: {error_string(code)} (code {code})")
+        self.code = int(code)
+
+
+def raise_on_error(rc: int, where: str) -> None:
+    if rc != 0:
+        raise KernelLaunchError(rc, where)
 
 
 class KernelStatusError(RuntimeError):
@@ -195,3 +208,32 @@ def check_status(device, where: str = "") -> None:
     if code != 0:
         t.zero_()
         raise KernelStatusError(f"mcsparse_b200 kernel status {code} ({where}): a bounded device-side wait expired")
+
+
+_status_polls: dict = {}
+
+
+def poll_status(device, where: str = "") -> None:
+    """Non-blocking health check for a point that runs once per step: looks at the copy of the status word
+    that the PREVIOUS call put in flight (raises KernelStatusError if it arrived non-zero, after clearing the
+    device word so that later launches are not aborted by the stale code), then enqueues a fresh copy to
+    pinned host memory on the current stream.  Never synchronises; an error surfaces one call late."""
+    import torch
+    t = status_word(device)
+    key = t.device.index
+    st = _status_polls.get(key)
+    if st is None:
+        st = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+        _status_polls[key] = st
+    if st["event"] is not None and st["event"].query():
+        code = int(st["host"][0])
+        if code != 0:
+            st["event"] = None
+            t.zero_()
+            raise KernelStatusError(f"mcsparse_b200 kernel status {code} ({where}): a bounded device-side wait expired")
+    elif st["event"] is not None:
+        return                                   # the previous copy is still in flight: look again next time
+    st["host"].copy_(t, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(t.device))
+    st["event"] = ev

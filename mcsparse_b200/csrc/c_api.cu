@@ -23,11 +23,6 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
-#if defined(MCS_TRACE)
-static long long* g_trace = nullptr;
-extern "C" void mcs_debug_set_trace(long long* t) { g_trace = t; }
-#endif
-
 static long long* g_clock_out = nullptr;
 
 extern "C" {
@@ -109,14 +104,13 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
     p.gather_len = (a->Sk + 127) / 128 * 128;       // every key tile of the sequence
   }
   if (negate && a->residual == nullptr) return MCS_ERR_NULL_POINTER;
+  if (a->flags & ~MCS_ATTN_OUT_GROUP_ORDER) return MCS_ERR_UNSUPPORTED;
+  p.out_group_order = (a->flags & MCS_ATTN_OUT_GROUP_ORDER) ? 1 : 0;
   p.out_sign = negate ? -1.f : 1.f;
   p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
   for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   p.clock_out = g_clock_out;
-#if defined(MCS_TRACE)
-  p.trace = g_trace;
-#endif
 
   if (a->dtype == MCS_DTYPE_E4M3) {
     if (a->scale_qk_log2 == nullptr || a->scale_v == nullptr) return MCS_ERR_NULL_POINTER;

@@ -115,31 +115,6 @@ struct Smem {
   static constexpr int kDynamic = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
 };
 
-#ifdef MCS_TRACE
-// Diagnostics build: per-role clock accumulators of CTA 0, written once at the end.
-// trace[role*16 + slot]; TR_BEGIN/TR_END bracket a region, TR_FLUSH stores the sums.
-#define TR_DECL long long tr_acc[12] = {0}; long long tr_t = 0; (void)tr_t
-#define TR_BEGIN() tr_t = clock64()
-#define TR_END(slot) do { const long long tr_n = clock64(); tr_acc[slot] += tr_n - tr_t; tr_t = tr_n; } while (0)
-#define TR_FLUSH(role, cond)                                                          \
-  do {                                                                                \
-    if (p.trace != nullptr && blockIdx.x == 0 && (cond))                              \
-      for (int tr_i = 0; tr_i < 12; ++tr_i) p.trace[(role) * 16 + tr_i] = tr_acc[tr_i]; \
-  } while (0)
-// timeline: clock of event `ev` at CTA-global tile `gg` (tiles TL_FIRST .. TL_FIRST+63 of CTA 0)
-#define TL_FIRST 32
-#define TL(ev, gg, cond)                                                                              \
-  do {                                                                                                \
-    if (p.trace != nullptr && blockIdx.x == 0 && (cond) && (gg) >= TL_FIRST && (gg) < TL_FIRST + 64)  \
-      p.trace[1024 + (ev) * 64 + ((gg) - TL_FIRST)] = clock64();                                      \
-  } while (0)
-#else
-#define TL(ev, gg, cond) do { } while (0)
-#define TR_DECL do { } while (0)
-#define TR_BEGIN() do { } while (0)
-#define TR_END(slot) do { } while (0)
-#define TR_FLUSH(role, cond) do { } while (0)
-#endif
 
 // One producer warp copies kRowsPerProducerWarp rows of D 16-bit elements into a swizzled
 // tile.  Lane (l % rows) holds the source row index of tile row (row0 + l); a negative
@@ -298,8 +273,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     int g = 0;      // tiles processed by this CTA so far
     int ic = 0;     // items processed by this CTA so far
     bool ok = true;
-    TR_DECL;
-    TR_BEGIN();
 
     constexpr int kHalf = D / 2;                 // output columns whose accumulator this stream rescales
     bool s_ready = false;       // next tile's score barrier was already complete when probed
@@ -317,12 +290,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 #pragma unroll 1
       for (int t = 0; t < it.T; ++t, ++g) {
         const int buf = g & 1;
-        TR_END(0);
         if (!s_ready) ok = mbar_wait(bar(BAR_S_FULL + buf), (g >> 1) & 1, p.status, 10);
         if (!ok) { fail_item = item; fail_t = t; fail_bar_done = false; break; }
         tc_fence_after();
-        TR_END(1);   // wait S_FULL
-        TL(x == 0 ? 7 : 10, g, lane == 0 && (warp & 3) == 0);
         // Copy this thread's 64 scores to registers and hand S[buf] back to the Q K^T issuer at once.
         const uint32_t tSx = tmem + kColS + buf * 128 + x * 64 + lane_addr;
         uint32_t sc[64];
@@ -338,10 +308,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           for (int i = 0; i < 64; ++i)
             if (i >= rem) sc[i] = 0xff800000u;
         }
-        TL(8, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // P[buf] was last read by P V of tile g-2: probe now, wait (if at all) just before the stores
         const bool p_free = g < 2 || mbar_test_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1);
-        TR_END(2);   // tmem ld
         // four independent chains of three-input maxima
         float mx0 = fmaxf(__uint_as_float(sc[0]), __uint_as_float(sc[1]));
         float mx1 = fmaxf(__uint_as_float(sc[2]), __uint_as_float(sc[3]));
@@ -384,13 +352,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
               tmem_st8(tOh + c * 8, r);
             }
           }
-          TR_END(4);   // raise (rare)
         }
         const float neg_m = kBias - m_run;
-        TL(17, g, x == 0 && lane == 0 && (warp & 3) == 0);
         if (!p_free) ok = mbar_wait(bar(BAR_PV_DONE + buf), ((g >> 1) - 1) & 1, p.status, 15);
         if (!ok) { fail_item = item; fail_t = t; fail_bar_done = true; break; }
-        TL(18, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // exp2, partial row sum, pack, store P: 16 values (8 or 4 columns) at a time
         const uint32_t tPx = tmem + kColP + buf * 64 + x * 32 + lane_addr;
         float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
@@ -423,26 +388,19 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           }
         }
         l_run += (ls0 + ls1) + (ls2 + ls3);
-        TR_END(5);   // softmax
-        TL(19, g, x == 0 && lane == 0 && (warp & 3) == 0);
         // probe the next tile's score barrier now, so that a satisfied wait costs nothing at the loop top
         s_ready = mbar_test_wait(bar(BAR_S_FULL + ((g + 1) & 1)), ((g + 1) >> 1) & 1);
         tmem_wait_st();
-        TL(20, g, x == 0 && lane == 0 && (warp & 3) == 0);
         tc_fence_before();
         warp_arrive(bar(BAR_P_READY + 2 * x + buf));
-        TR_END(6);   // st + arrive
-        TL(x == 0 ? 9 : 11, g, lane == 0 && (warp & 3) == 0);
         if (t == it.T - 1) {
           // Last tile done: publish this stream's partial row sum (and the shared max) for the epilogue
           // warps, once they have read the previous item's (normally long true).
           if (ic > 0) ok = mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 13);
           if (!ok) { fail_item = item; fail_t = t; fail_bar_done = true; break; }
-          TR_END(9);   // wait previous O_EMPTY
           stats[x * 128 + r_in] = l_run;
           if (x == 0) stats[256 + r_in] = m_run;
           warp_arrive(bar(BAR_STATS));
-          TR_END(10);  // stats store + arrive
         }
       }
       if (!ok) break;
@@ -464,7 +422,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         item += gridDim.x;
       }
     }
-    TR_FLUSH(x, lane == 0 && (warp & 3) == 0);
     tc_fence_before();
   } else if (warp < kMmaWarp) {
     // =====================================================================
@@ -483,8 +440,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     int slot = 0, slot_phase = 0;   // ring position; the phase flips every wrap
     bool wrapped = false;
     bool ok = true;
-    TR_DECL;
-    TR_BEGIN();
 
     auto enter_item = [&](int item, int ic) {
       // called once per item when the K cursor reaches it: request Q, warm L2 for this item's residual
@@ -517,8 +472,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       cp_async_arrive_noinc(bar(BAR_Q_FULL + qbuf));
     };
 
-    int tl_k = 0, tl_v = 0;   // diagnostics: CTA-global tile numbers of the K and V cursors
-    (void)tl_k; (void)tl_v;
     // per-item constants of a cursor
     struct Cur {
       int item, ic, t, T, b, h;
@@ -547,17 +500,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
     };
     auto load_tile = [&](const uint8_t* lane_src, size_t row_bytes, int idx, bool is_v) {
-      TR_END(0);
       if (wrapped) ok = ok && mbar_wait(bar(BAR_EMPTY + slot), slot_phase ^ 1, p.status, 20);
       if (!ok) return;
-      TR_END(1);   // wait for a free ring slot
-      TL(is_v ? 14 : 12, is_v ? tl_v : tl_k, pw == 0 && lane == 0);
       // raw index, clamped only here: the global load issued one step earlier stays in flight until now
       warp_gather_rows<RB>(sRing(slot), row0, min(max(idx, 0), p.Sk - 1), lane_src, row_bytes, lane);
       cp_async_arrive_noinc(bar(BAR_FULL + slot));
-      TR_END(2);   // issue the tile's cp.async
-      TL(is_v ? 15 : 13, is_v ? tl_v : tl_k, pw == 0 && lane == 0);
-      if (is_v) ++tl_v; else ++tl_k;
       if (++slot == kRing) { slot = 0; slot_phase ^= 1; wrapped = true; }
     };
 
@@ -626,7 +573,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     }
     cp_async_wait_all();
     tc_fence_before();
-    TR_FLUSH(2, pw == 0 && lane == 0);
   } else if (warp >= kEpiWarp0) {
     // =====================================================================
     // epilogue warps: one per tensor-memory lane group, thread == query row.
@@ -667,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       if (r_in < it.rows_valid) {
         const int row = it.row_base + r_in;               // position in (permuted) query order
         long long orow = row;
-        if (p.perm != nullptr) orow = p.perm[(size_t)it.bh * p.Sq + row];
+        if (p.perm != nullptr && !p.out_group_order) orow = p.perm[(size_t)it.bh * p.Sq + row];
         uint8_t* obase = reinterpret_cast<uint8_t*>(p.out);
         long long lrow = orow;
         if (p.n_out_peers > 0) {
@@ -782,8 +728,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       constexpr uint32_t kLboK = (16u >> 4) << 16;       // K-major operands (Q, K): LBO unused
       bool ok = true;
       int slot = 0, phase = 0;                           // ring position of the next K entry
-      TR_DECL;
-      TR_BEGIN();
       int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
       // optional telemetry (mcs_set_clock_buffer): SM cycles and nanoseconds this CTA's tile loop ran, i.e.
       // the SM clock under the kernel's own load, which no host-side poll can resolve
@@ -794,18 +738,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
 #pragma unroll 1
       while (item < n_items) {
         const int qbuf = ic & 1, buf = g & 1;
-        TL(16, g, lane == 0);
         const bool k_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
         const bool s_free = g < 2 || mbar_test_wait(bar(BAR_S_FREE + buf), ((g >> 1) - 1) & 1);
-        TR_END(0);
         if (t == 0 && !mbar_wait(bar(BAR_Q_FULL + qbuf), (ic >> 1) & 1, p.status, 31)) { ok = false; break; }
         if (!wait_if(k_ready, bar(BAR_FULL + slot), phase, 30)) { ok = false; break; }
-        TR_END(1);   // wait K (and Q) full
         if (!wait_if(s_free, bar(BAR_S_FREE + buf), ((g >> 1) - 1) & 1, 35)) { ok = false; break; }
-        TR_END(4);   // wait score buffer free (softmax of tile g-2 has copied its scores out)
         fence_proxy_async_smem();
         tc_fence_after();
-        TL(0, g, lane == 0);
         const uint32_t tS = tmem + kColS + buf * 128;
         const uint32_t qlo = ((sQ(qbuf) & 0x3FFFFu) >> 4) | kLboK;
         const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboK;
@@ -818,15 +757,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
             else mma_f16_ss(tS, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
           }
         }
-        TR_END(2);   // issue QK MMAs
-        TL(1, g, lane == 0);
         if (leader) {
           tc_commit(bar(BAR_EMPTY + slot));
           tc_commit(bar(BAR_S_FULL + buf));
           if (t == T - 1) tc_commit(bar(BAR_Q_EMPTY + qbuf));
         }
-        TR_END(3);   // QK commits
-        TL(2, g, lane == 0);
         // next K entry: 0 -> 1, then +2
         const int step = g == 0 ? 1 : 2;
         slot += step;
@@ -844,8 +779,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         p.clock_out[1] = static_cast<long long>(globaltimer_ns() - clk_g0);
         p.clock_out[2] = g;
       }
-      TR_END(0);
-      TR_FLUSH(3, lane == 0);
       if (!ok) {
         // error path: let outstanding MMAs retire before tensor memory is released
         if (leader) tc_commit(bar(BAR_DRAIN));
@@ -858,26 +791,19 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       bool ok = true;
       int slot = 2, phase = 0;                           // ring position of the next V entry (V(0) = entry 2)
       int item = blockIdx.x, ic = 0, t = 0, T = decode_item(p, item).T, g = 0;
-      TR_DECL;
-      TR_BEGIN();
 #pragma unroll 1
       while (item < n_items) {
         const int buf = g & 1;
-        TR_END(0);
-        TL(3, g, lane == 0);
         const bool v_ready = mbar_test_wait(bar(BAR_FULL + slot), phase);
         const bool pa_ready = mbar_test_wait(bar(BAR_P_READY + buf), (g >> 1) & 1);
         const bool pb_ready = mbar_test_wait(bar(BAR_P_READY + 2 + buf), (g >> 1) & 1);
         if (!wait_if(v_ready, bar(BAR_FULL + slot), phase, 34)) { ok = false; break; }
         if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) { ok = false; break; }
-        TR_END(1);   // wait V (and O_EMPTY)
         const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
         fence_proxy_async_smem();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (g >> 1) & 1, 33)) { ok = false; break; }
-          TR_END(2);   // wait P
-          if (x == 0) TL(4, g, lane == 0);
           tc_fence_after();
           const uint32_t tP = tmem + kColP + buf * 64 + x * 32;
           const uint32_t tO = tmem + kColO;
@@ -896,15 +822,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           }
         }
         if (!ok) break;
-        TR_END(3);   // issue PV MMAs
-        TL(5, g, lane == 0);
         if (leader) {
           tc_commit(bar(BAR_EMPTY + slot));
           tc_commit(bar(BAR_PV_DONE + buf));
           if (t == T - 1) tc_commit(bar(BAR_O_FULL));
         }
-        TR_END(4);   // PV commits
-        TL(6, g, lane == 0);
         slot += 2;
         if (slot >= kRing) { slot -= kRing; phase ^= 1; }
         ++g;
@@ -915,7 +837,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
           if (item < n_items) T = decode_item(p, item).T;
         }
       }
-      TR_FLUSH(4, lane == 0);
       if (!ok) {
         if (leader) tc_commit(bar(BAR_DRAIN + 1));
         mbar_wait_quiet(bar(BAR_DRAIN + 1), 0, 1 << 20);

@@ -21,7 +21,6 @@ struct GatherAttnParams {
   int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], r_stride[3];
   int B, Sq, Sk, H, D, M, gather_len, group_rows;
   float scale_log2;  // softmax_scale * log2(e)
-  long long* trace;  // diagnostics builds only (MCS_TRACE): per-role event clocks of CTA 0
   long long* clock_out;  // optional: {SM cycles, nanoseconds, tiles} of CTA 0's tile loop (mcs_set_clock_buffer)
   // sequence-sharded output (Ulysses): row r' of the output goes to out_peer[r' / out_rows_per_peer] at local
   // row r' % out_rows_per_peer (peer or local memory alike)
@@ -30,6 +29,7 @@ struct GatherAttnParams {
   int dense;                // 1: no index list, every query group attends to all Sk keys (tail of the last tile masked)
   int n_out_peers;          // 0 = not sharded
   int out_rows_per_peer;
+  int out_group_order;      // 1: with perm, output and lse rows stay in permuted (group) order
 };
 
 // Tensor maps of K and V for the dense mode (TMA tile loads of 128 contiguous key rows): 4-D maps with the

@@ -459,7 +459,7 @@ Plan make_plan(int BH, int N, int C) {
       ls.items += (size + kChunkRows - 1) / kChunkRows;
       max_size = std::max(max_size, size);
     }
-    ls.pad = next_pow2(max_size);
+    ls.pad = std::max(next_pow2(max_size), 8);   // the projection kernel works on whole groups of kProjRows = 8 slots
     pl.shape.push_back(ls);
     pl.max_items = std::max(pl.max_items, ls.items);
     pl.key_stride = std::max(pl.key_stride, (size_t)ls.nodes * ls.pad);

@@ -17,10 +17,24 @@ buffers and the kernels only ever read local memory.
 
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+import math
+from typing import Callable, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
+
+# cp_calls: went through the Ulysses exchange; local_calls: did not (one GPU, or a call that came without a
+# context-parallel configuration).  Same two counters as the reference (context_parallel.py:64-73).
+_STATS = {"cp_calls": 0, "local_calls": 0}
+
+
+def get_cp_stats() -> dict:
+    return dict(_STATS)
+
+
+def reset_cp_stats() -> None:
+    for k in _STATS:
+        _STATS[k] = 0
 
 
 class UlyssesReshard:
@@ -215,8 +229,7 @@ def ulysses_scatter(src: torch.Tensor, dst_ptrs: Sequence[int], rank: int, rows:
     fn = _lib.lib().mcs_ulysses_scatter_dma if dma else _lib.lib().mcs_ulysses_scatter
     rc = fn(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows), int(seg_bytes), int(seg_stride_bytes),
             int(src_row_bytes), C.c_void_p(stream))
-    if rc != 0:
-        raise RuntimeError(f"mcs_ulysses_scatter{'_dma' if dma else ''}: {_lib.error_string(rc)} (code {rc})")
+    _lib.raise_on_error(rc, f"mcs_ulysses_scatter{'_dma' if dma else ''}")
 
 
 class PeerBuffers:
@@ -361,3 +374,170 @@ class UlyssesFusedAttention:
         with torch.cuda.graph(graph):
             out = self.forward(q, k, v, attn_fn)
         return graph, out
+
+
+# =====================================================================================================
+# with_ulysses_sparse: the dispatch wrapper of the reference (context_parallel.py:154-231)
+# =====================================================================================================
+def _make_dense(fa3: bool) -> Callable:
+    """Dense attention on BTHD tensors used by the sparse dispatch for its full layers / steps.  The
+    reference chooses between FA3 and SDPA by ``fa3`` (context_parallel.py:76-88); here both spell this
+    package's dense mode, which accepts different query and key lengths."""
+    def dense(q, k, v):
+        from mcsparse_b200.kernels.flash_mcsa.ops.full_attn import full_attention
+        return full_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).contiguous()
+    return dense
+
+
+def _make_kernel(kind: str, cfg: dict, dense: Callable) -> Callable:
+    """The attention itself on full-sequence, head-local BTHD tensors: ``kernel(q, k, v, out_peers=None)``.
+
+    "mcsa_token" builds the token-sparse dispatch with the original dispatch replaced by ``dense``;
+    "dense" routes the dense arm through the same exchange (context_parallel.py:91-151)."""
+    if kind == "mcsa_token":
+        from mcsparse_b200.h3 import token_sparse_dispatch as tsd
+        inner = cfg.get("_inner_dispatch")
+        if inner is None:
+            known = ("sink_tokens", "num_layers", "num_steps", "topk", "dense_steps", "dense_layers", "calibrate_every",
+                     "calibrate_steps", "pca_reorder", "pca_pow_iters", "pca_proj_dim", "bias_correction", "selection_mode",
+                     "topp", "adaptive_layers", "use_chunk_selector", "chunk_selector_size", "offload_indices",
+                     "cache_offload", "offload_prefetch_ahead", "update_steps", "approx_steps", "full_attn_impl",
+                     "allow_no_sink", "min_seq_len", "ticks_per_step")
+            kw = {k: cfg[k] for k in known if k in cfg}
+            kw.setdefault("sink_tokens", 0)
+            kw.setdefault("topk", 0.25)
+            inner = tsd.make_mcsa_token_dispatch(lambda q, k, v, *a, **k2: dense(q, k, v), **kw)
+
+        def kernel(q, k, v, out_peers=None):
+            # parallel_config=None on purpose: past the exchange this is an ordinary full-sequence problem
+            if out_peers is None:
+                return inner(q, k, v, None, 0.0, False, None, False, None, backend=None, parallel_config=None)
+            return inner(q, k, v, None, 0.0, False, None, False, None, backend=None, parallel_config=None,
+                         out_peers=out_peers)
+        return kernel
+    if kind == "dense":
+        def kernel(q, k, v, out_peers=None):
+            return dense(q, k, v)
+        return kernel
+    raise ValueError(f"kind must be 'mcsa_token' or 'dense'; got {kind!r}")
+
+
+def _cp_group(cp):
+    """Process group of the Ulysses dimension of a context-parallel configuration (diffusers keeps a device
+    mesh on it; a plain ``ulysses_group`` attribute is accepted as well), default: the world."""
+    g = getattr(cp, "ulysses_group", None)
+    if g is not None:
+        return g
+    mesh = getattr(cp, "_ulysses_mesh", None)
+    if mesh is not None and hasattr(mesh, "get_group"):
+        return mesh.get_group()
+    return dist.group.WORLD
+
+
+class UlyssesRoute:
+    """Runs ``kernel`` between the two reshards for one (shape, group); built on first use.
+
+    CUDA, batch 1, 16-bit tensors and peer-mappable memory: the fused path (``UlyssesFusedAttention``) -
+    scatter kernel in front, and when the kernel call ends in the sparse attention its epilogue stores
+    the rows straight into the owners' shards; a call that returns a tensor instead (anchor step, dense
+    layer) is brought back by a library all-to-all.  Everything else (CPU tensors under gloo, batches):
+    ``UlyssesReshard`` with library all-to-alls on both sides."""
+
+    def __init__(self, group, q: torch.Tensor, fused: Optional[bool] = None):
+        B, Ls, H, D = q.shape
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.shape = (B, Ls, H, D, q.dtype, q.device)
+        L = Ls * self.world
+        self.reshard = UlyssesReshard(group, L, H, D, q.dtype, q.device, batch=B)
+        can_fuse = q.is_cuda and B == 1 and q.dtype in (torch.bfloat16, torch.float16) and self.world > 1
+        self.fused = None
+        if can_fuse and fused is not False:
+            try:
+                self.fused = UlyssesFusedAttention(group, L, H, D, q.dtype, q.device, chunks=1, dma_from_chunk=None)
+            except Exception:
+                if fused:
+                    raise
+                self.fused = None
+
+    def run(self, kernel: Callable, q, k, v):
+        if self.fused is None:
+            qh, kh, vh = self.reshard.seq_to_head(q.contiguous(), k.contiguous(), v.contiguous())
+            return self.reshard.head_to_seq(kernel(qh, kh, vh).contiguous())
+        u = self.fused
+        stored = []
+
+        def attn(qh, kh, vh, h0, h1, out_peers):
+            o = kernel(qh, kh, vh, out_peers=out_peers)
+            stored.append(o)
+
+        out = u.forward(q.contiguous(), k.contiguous(), v.contiguous(), attn)
+        if stored and stored[0] is not None:
+            # the kernel returned a head-sharded tensor (anchor step, dense layer): library exchange back
+            return self.reshard.head_to_seq(stored[0].contiguous())
+        return out
+
+
+def with_ulysses_sparse(original_dispatch: Callable, *, kind: str, fa3: bool = False, **cfg) -> Callable:
+    """Wrap an attention dispatch so that the sparse kernel runs after the Ulysses exchange.
+
+    Same contract as the reference's wrapper (context_parallel.py:154-231): unsupported arguments go to
+    ``original_dispatch`` untouched; without a ``parallel_config`` (or without a context-parallel part in
+    it) the kernel runs locally and ``local_calls`` counts; ``ring_degree > 1`` raises ``ValueError``
+    because no rank ever holds a whole KV sequence under ring attention; with Ulysses the sequence shards
+    are exchanged for head shards, the kernel runs on full sequences of the local heads with rank-local
+    metadata, and the result returns to sequence shards (``cp_calls``).  The reference hands its kernel to
+    diffusers' ``_templated_context_parallel_attention`` as ``forward_op``; this wrapper owns the exchange
+    (:class:`UlyssesRoute`).  ``cfg`` are the arguments of ``make_mcsa_token_dispatch``; ``fused`` (True /
+    False / None = decide by device) picks the exchange implementation.
+    """
+    fused = cfg.pop("fused", None)
+    dense = cfg.pop("_dense", None) or _make_dense(fa3)
+    kernel = _make_kernel(kind, cfg, dense)
+    routes: dict = {}
+
+    def forward_op(ctx, query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, enable_gqa=False,
+                   return_lse=False, _save_ctx=True, _parallel_config=None):
+        """The kernel in the calling convention of a diffusers context-parallel forward op, for a caller that
+        drives the exchange itself (context_parallel.py:165-176)."""
+        if return_lse:
+            raise ValueError("sparse CP forward_op produces no LSE, so it cannot serve ring attention. "
+                             "Use ulysses_degree with ring_degree=1.")
+        _STATS["cp_calls"] += 1
+        return kernel(query.contiguous(), key.contiguous(), value.contiguous())
+
+    def dispatch(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, enable_gqa=False,
+                 attention_kwargs=None, *, backend=None, parallel_config=None):
+        supported = (attn_mask is None and not is_causal and dropout_p == 0.0 and not enable_gqa
+                     and getattr(query, "ndim", 0) == 4
+                     and (scale is None or math.isclose(float(scale), 1.0 / math.sqrt(query.shape[-1])))
+                     and tuple(query.shape) == tuple(key.shape) == tuple(value.shape)
+                     and (bool(getattr(query, "is_cuda", False)) or cfg.get("_allow_cpu", False)))
+        if not supported:
+            return original_dispatch(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa,
+                                     attention_kwargs, backend=backend, parallel_config=parallel_config)
+        cp = None if parallel_config is None else getattr(parallel_config, "context_parallel_config", None)
+        if cp is None:
+            _STATS["local_calls"] += 1
+            return kernel(query.contiguous(), key.contiguous(), value.contiguous())
+        if getattr(cp, "ring_degree", 1) > 1:
+            raise ValueError(f"ring_degree={cp.ring_degree}: ring attention hands each rank rotating KV chunks, so a "
+                             "sparse kernel never sees a whole KV sequence and its routing would be wrong. "
+                             "Use ulysses_degree instead.")
+        if getattr(cp, "ulysses_degree", 1) <= 1:
+            _STATS["local_calls"] += 1
+            return kernel(query.contiguous(), key.contiguous(), value.contiguous())
+        group = _cp_group(cp)
+        key_ = (tuple(query.shape), query.dtype, str(query.device), id(group))
+        route = routes.get(key_)
+        if route is None:
+            route = routes[key_] = UlyssesRoute(group, query, fused=fused)
+        _STATS["cp_calls"] += 1
+        return route.run(kernel, query, key, value)
+
+    dispatch.forward_op = forward_op
+    return dispatch
+
+
+__all__ = ["get_cp_stats", "reset_cp_stats", "with_ulysses_sparse", "UlyssesReshard", "UlyssesSparseAttention",
+           "UlyssesFusedAttention", "UlyssesRoute", "PeerBuffers", "ulysses_scatter"]

@@ -17,7 +17,9 @@ makes around the kernel into the kernel itself:
               ``i`` of a head is ``q[b, perm[i], h]`` and output row ``i`` is written to
               ``out[b, perm[i], h]`` (reference: apply_perm before / invert_perm after,
               token_sparse.py:1057-1060);
-``group_rows`` query rows per index group (reference tile: 128).
+``group_rows`` query rows per index group (reference tile: 128);
+``out_group_order`` with ``perm``: only Q is read through the permutation, output and lse rows stay in
+              the permuted order (what the anchor step's residual construction works in).
 """
 
 from __future__ import annotations
@@ -161,8 +163,7 @@ def _launch(args: "_lib.GatherAttnArgs", device, where: str, out_peers=None, sub
         ptrs, rows_per_peer, _ = out_peers
         table = (C.c_void_p * len(ptrs))(*[int(x) for x in ptrs])
         rc = _lib.lib().mcs_gather_attn_fwd_sharded(args, table, len(ptrs), int(rows_per_peer), stream)
-    if rc != 0:
-        raise RuntimeError(f"{where}: {_lib.error_string(rc)} (code {rc})")
+    _lib.raise_on_error(rc, f"{where}")
     if _lib.check_enabled():
         _lib.check_status(device, where)
 
@@ -204,6 +205,7 @@ def flash_attn_gather_kv_func(
     group_rows: int = 128,
     out_peers=None,
     residual_minus_attention: bool = False,
+    out_group_order: bool = False,
 ):
     """Forward-only token-level sparse gather-KV attention on B200.
 
@@ -279,6 +281,10 @@ def flash_attn_gather_kv_func(
     if out_peers is not None:
         args.out = None
         args.o_stride[0], args.o_stride[1], args.o_stride[2] = (int(x) for x in out_peers[2])
+    if out_group_order and perm is not None:
+        if out_peers is not None:
+            raise ValueError("out_group_order and out_peers cannot be combined")
+        args.flags = _lib.MCS_ATTN_OUT_GROUP_ORDER
     if residual_minus_attention and residual is None:
         raise ValueError("residual_minus_attention needs residual (the dense attention output, (B,H,Sq,D))")
     _launch(args, device, "flash_attn_gather_kv_func", out_peers, subtract=residual_minus_attention)

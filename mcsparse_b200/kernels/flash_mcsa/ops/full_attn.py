@@ -31,7 +31,8 @@ def describe(resolved: str) -> str:
 
 
 def _dense(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float], want_lse: bool,
-           residual: Optional[Tensor] = None, perm: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
+           residual: Optional[Tensor] = None, perm: Optional[Tensor] = None,
+           group_order: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
     from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import interface as itf
     if q.dim() != 4 or k.shape != v.shape or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
         raise ValueError(f"expected (B, H, L, D) tensors, got q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
@@ -51,10 +52,11 @@ def _dense(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float], want_lse: bo
     args = itf._fill_args(qv.detach(), kv.detach(), vv.detach(), ov, lse, gi_dummy, None, residual, perm, 128, 128,
                           dtype_code, scale)
     args.gi = None
+    if group_order and perm is not None:
+        args.flags = _lib.MCS_ATTN_OUT_GROUP_ORDER
     stream = torch.cuda.current_stream(q.device).cuda_stream
     rc = _lib.lib().mcs_dense_attn_fwd(args, stream)
-    if rc != 0:
-        raise RuntimeError(f"mcs_dense_attn_fwd: {_lib.error_string(rc)} (code {rc})")
+    _lib.raise_on_error(rc, f"mcs_dense_attn_fwd")
     if _lib.check_enabled():
         _lib.check_status(q.device, "full_attention")
     return out, lse
@@ -65,7 +67,12 @@ def full_attention(q: Tensor, k: Tensor, v: Tensor, resolved: str = "native", sc
     return _dense(q, k, v, scale, want_lse=False)[0]
 
 
-def full_attention_with_lse(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None) -> Tuple[Tensor, Tensor]:
-    """Dense attention output (B, H, L_q, D) in q's dtype and its LSE (B, H, L_q) fp32 from one kernel launch."""
-    out, lse = _dense(q, k, v, scale, want_lse=True)
+def full_attention_with_lse(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, *,
+                            perm: Optional[Tensor] = None, group_order: bool = False) -> Tuple[Tensor, Tensor]:
+    """Dense attention output (B, H, L_q, D) in q's dtype and its LSE (B, H, L_q) fp32 from one kernel launch.
+
+    ``perm`` ((B*H, L_q) int64, an addition to the reference signature) makes the kernel read query row i from
+    ``q[perm[i]]``; output and LSE row i then go back to position ``perm[i]``, or stay at position i (the
+    permuted, "group" order the anchor step works in) with ``group_order``."""
+    out, lse = _dense(q, k, v, scale, want_lse=True, perm=perm, group_order=group_order)
     return out, lse

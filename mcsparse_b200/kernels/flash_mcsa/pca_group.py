@@ -122,8 +122,7 @@ def _perm_rows(x: Tensor, perm: Tensor, invert: bool) -> Tensor:
     stream = torch.cuda.current_stream(x.device).cuda_stream
     rc = fn(x.data_ptr(), out.data_ptr(), perm.contiguous().data_ptr(), BH, N, D * es,
             x.stride(0) * es, x.stride(1) * es, out.stride(0) * es, out.stride(1) * es, stream)
-    if rc != 0:
-        raise RuntimeError(f"perm rows: {_lib.error_string(rc)} (code {rc})")
+    _lib.raise_on_error(rc, f"perm rows")
     return out
 
 

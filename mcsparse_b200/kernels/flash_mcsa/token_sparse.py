@@ -117,8 +117,7 @@ def select_topk_with_sinks(scores: torch.Tensor, k_total: int, sink_ranges=None,
     rc = _lib.lib().mcs_topk_select(scores.data_ptr(), out.data_ptr(),
                                     None if sink_t is None else sink_t.data_ptr(), len(sinks), rows, L,
                                     int(k_total), stream)
-    if rc != 0:
-        raise RuntimeError(f"select_topk_with_sinks: {_lib.error_string(rc)} (code {rc})")
+    _lib.raise_on_error(rc, f"select_topk_with_sinks")
     if _lib.check_enabled():
         _lib.check_status(scores.device, "select_topk_with_sinks")
     return out
@@ -157,6 +156,67 @@ def _select_topk_tokens(token_probs, topk_ratio, tile_n=128, ds_k=1, orig_L_K=No
     return gi, lengths
 
 
+def _compute_adaptive_topk_token(token_probs, base_topk, layer_t=None):
+    """Per-head budgets from the retained mass (token_sparse.py:695-738): heads whose top-k already holds more of
+    the mass get less budget.  Returns (B, H) fractions."""
+    B, H, M, L_K = token_probs.shape
+    k = min(max(1, int(base_topk * L_K)), L_K)
+    scores = token_probs.float()
+    gi = select_topk_with_sinks(scores, k)                                   # (B,H,M,k) ascending indices
+    kept = scores.gather(-1, gi.long()).sum(-1)
+    recall = (kept / scores.sum(-1).clamp(min=1e-8)).mean(-1)                # (B, H)
+    order = recall.argsort(dim=-1)
+    ranks = torch.zeros_like(order)
+    ranks.scatter_(-1, order, torch.arange(H, device=scores.device).expand(B, H))
+    t = ranks.float() / max(H - 1, 1)
+    per_head = base_topk * ((1.0 + 0.5 * layer_t - 0.5 * t) if layer_t is not None else (1.5 - t))
+    return per_head.clamp(min=1.0 / L_K, max=1.0)
+
+
+def _chunked_online_topk(q, k, lse, BLKQ, scale, topk_k, tile_n=128, chunk_size=None, perm=None):
+    """Selection without the full (B,H,M,L_K) score tensor in memory (token_sparse.py:602-687).
+
+    The reference walks the keys in chunks and keeps a running top-k of bf16-rounded scores.  Here the
+    mass kernel writes fp32 scores for a few heads at a time (the bound on memory is the same idea,
+    cut along heads instead of keys: at most about ``chunk_size * 2^16`` scores at once) and the exact selection
+    kernel picks the top ``topk_k`` of each row, ascending.  Returns (B,H,M,topk_k) int32."""
+    B, H, Lq, D = q.shape
+    L_K = k.shape[2]
+    M = math.ceil(Lq / BLKQ)
+    k_sel = min(((topk_k + tile_n - 1) // tile_n) * tile_n, L_K)
+    budget = int(chunk_size or 16384) << 16
+    hc = max(1, min(H, budget // max(1, M * L_K)))
+    gi = torch.empty(B, H, M, k_sel, dtype=torch.int32, device=q.device)
+    for h0 in range(0, H, hc):
+        h1 = min(H, h0 + hc)
+        pm = None if perm is None else perm.view(B, H, Lq)[:, h0:h1].reshape(-1, Lq)
+        mass = group_mass(q[:, h0:h1], k[:, h0:h1], lse[:, h0:h1], group_rows=BLKQ, scale=scale, perm=pm)
+        gi[:, h0:h1] = select_topk_with_sinks(mass, k_sel)
+        del mass
+    return gi
+
+
+def _approx_select(q, k, cfg, perm=None):
+    """Selection of an ``approx`` step (token_sparse.py:1344-1406): score every key against the mean query of
+    each group (no LSE needed), keep the top budget, ascending.  The (M x D) x (D x L_K) product per head is a
+    plain library GEMM; the selection is this package's kernel on the fp32 scores."""
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import apply_perm_bhld
+    B, H, L, D = q.shape
+    L_K = k.shape[2]
+    M = math.ceil(L / cfg.BLKQ)
+    q_grp = q if perm is None else apply_perm_bhld(q, perm)
+    if M * cfg.BLKQ > L:
+        q_grp = torch.nn.functional.pad(q_grp, (0, 0, 0, M * cfg.BLKQ - L))
+    q_mean = q_grp.reshape(B, H, M, cfg.BLKQ, D).float().mean(dim=3).to(q.dtype)
+    n = max(1, int(cfg.topk * L_K))
+    k_sel = min(((n + cfg.tile_n - 1) // cfg.tile_n) * cfg.tile_n, L_K)
+    gi = torch.empty(B, H, M, k_sel, dtype=torch.int32, device=q.device)
+    for h in range(H):                                   # one head at a time bounds the score tensor
+        scores = torch.matmul(q_mean[:, h], k[:, h].transpose(-1, -2)).float()
+        gi[:, h] = select_topk_with_sinks(scores.contiguous(), k_sel)
+    return gi
+
+
 # =============================================================================================
 # Host-side state of token-sparse attention: configuration, per-layer cache, step modes.
 # Mirrors TokenSparseConfig (token_sparse.py:104-198), TokenSparseCache (:200-547, mode :233-247),
@@ -180,21 +240,27 @@ class TokenSparseConfig:
     sink_ranges: Optional[List[Tuple[int, int]]] = None
     calibrate_steps: Optional[List[int]] = None
     update_steps: Optional[List[int]] = None
+    approx_steps: Optional[List[int]] = None
     full_steps: Optional[List[int]] = None
     full_layers: List[int] = field(default_factory=list)
     share_lse: bool = False
     cal_downsample: Union[int, Tuple[int, int]] = 1
+    adaptive_heads: bool = False
+    adaptive_layers: bool = False
+    use_chunk_selector: bool = False
+    chunk_selector_size: int = 16384
     bias_correction: bool = False
     pca_reorder: bool = False
     pca_pow_iters: int = 4
     pca_seed: int = 0
+    pca_proj_dim: Optional[int] = None
 
     def __post_init__(self):
         assert 0 < self.topk <= 1.0
         assert self.selection_mode in ('topk', 'topp', 'topk_topp'), \
             f"selection_mode must be 'topk', 'topp', or 'topk_topp', got '{self.selection_mode}'"
-        if self.selection_mode != 'topk':
-            raise NotImplementedError("only selection_mode='topk' runs on the accelerated path")
+        if self.selection_mode in ('topp', 'topk_topp'):
+            assert self.topp is not None and 0 < self.topp <= 1.0, f"selection_mode='{self.selection_mode}' requires topp"
         assert self.BLKQ == 128
         assert self.tile_n == 128
         if isinstance(self.cal_downsample, (list, tuple)):
@@ -203,22 +269,33 @@ class TokenSparseConfig:
             ds = (int(self.cal_downsample),) * 2
         if ds != (1, 1):
             raise NotImplementedError("cal_downsample > 1 is not part of the accelerated path")
+        if self.pca_proj_dim is not None:
+            raise NotImplementedError("pca_proj_dim is not part of the accelerated path")
         self._cal_ds_q, self._cal_ds_k = ds
         self._calibrate_set = set(self.calibrate_steps) if self.calibrate_steps else None
         self._update_set = set(self.update_steps) if self.update_steps else None
+        self._approx_set = set(self.approx_steps) if self.approx_steps else None
         self._full_set = set(self.full_steps) if self.full_steps else None
         if self.sink_ranges:
             for start, end in self.sink_ranges:
                 assert 0 <= start < end, f"Invalid sink_ranges interval: ({start}, {end})"
         if self.pca_reorder:
             assert not self.share_lse, "pca_reorder is incompatible with share_lse"
+        assert self.chunk_selector_size > 0 and self.chunk_selector_size % self.tile_n == 0
+
+
+# modes in which the permutation is renewed together with the selection (token_sparse.py:984); an update
+# step keeps it because the cached per-query LSE is in the order of the anchor step
+_SELECTION_RECOMPUTE_MODES = ('calibrate', 'full_calibrate', 'approx')
 
 
 class TokenSparseCache:
     """Per-layer state carried between denoising steps: permutation, indices, LSE, residual."""
 
-    def __init__(self, config: TokenSparseConfig):
+    def __init__(self, config: TokenSparseConfig, layer_idx: int = 0, layer_t: Optional[float] = None):
         self.config = config
+        self._layer_idx = layer_idx
+        self.layer_t = layer_t             # normalised depth in [0, 1] for adaptive_layers, else None
         self._step_count = 0
         self._cached_lse = None
         self._cached_indices = None
@@ -243,6 +320,8 @@ class TokenSparseCache:
             return 'full'
         if c._calibrate_set and s in c._calibrate_set:
             return 'calibrate'
+        if c._approx_set and s in c._approx_set:
+            return 'approx'
         if c._update_set and s in c._update_set:
             return 'update'
         if not self.has_cache:
@@ -253,7 +332,7 @@ class TokenSparseCache:
         self._step_count += 1
 
     def reset(self) -> None:
-        self.__init__(self.config)
+        self.__init__(self.config, self._layer_idx, self.layer_t)
 
     def residual_if_valid(self):
         """The cached residual, unless it belongs to an older permutation (token_sparse.py:505-521)."""
@@ -265,14 +344,16 @@ class TokenSparseCache:
         return self._cached_residual
 
 
-def dense_attention_with_lse(q, k, v, scale):
+def dense_attention_with_lse(q, k, v, scale, perm=None, group_order: bool = False):
     """Dense attention output and natural-log LSE on (B,H,L,D) tensors: the input of the anchor step.
 
     The reference calls FA3 here (ops/full_attn.py:88-121); this is the package's own attention kernel in
-    dense mode, on strided views of the (B,H,L,D) tensors (no layout copies).
+    dense mode, on strided views of the (B,H,L,D) tensors (no layout copies).  With ``perm`` and
+    ``group_order`` the queries are read through the permutation and output and LSE come back in the
+    permuted (group) order, which replaces the gathered copy of Q in front of the dense pass.
     """
     from mcsparse_b200.kernels.flash_mcsa.ops.full_attn import full_attention_with_lse
-    return full_attention_with_lse(q, k, v, scale)
+    return full_attention_with_lse(q, k, v, scale, perm=perm, group_order=group_order)
 
 
 class TokenSparseBackend:
@@ -281,17 +362,48 @@ class TokenSparseBackend:
     def __init__(self, config: TokenSparseConfig):
         self.config = config
 
-    def _sparse(self, q, k, v, gi, gl, scale, residual, perm, subtract: bool = False):
+    def _sparse(self, q, k, v, gi, gl, scale, residual, perm, subtract: bool = False, out_peers=None,
+                group_order: bool = False):
         from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import flash_attn_gather_kv_func
         # (B,H,L,D) storage viewed as (B,L,H,D): no copies, the kernel takes the strides
-        out = torch.empty_like(q)
+        out = None if out_peers is not None else torch.empty_like(q)
         flash_attn_gather_kv_func(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), gi, softmax_scale=scale,
-                                  gather_kv_lengths=gl, out=out.transpose(1, 2), residual=residual, perm=perm,
-                                  residual_minus_attention=subtract)
+                                  gather_kv_lengths=gl, out=None if out is None else out.transpose(1, 2),
+                                  residual=residual, perm=perm, residual_minus_attention=subtract, out_peers=out_peers,
+                                  out_group_order=group_order)
         return out
 
-    def forward(self, cache: TokenSparseCache, q, k, v, scale: Optional[float] = None):
-        from mcsparse_b200.kernels.flash_mcsa.pca_group import apply_perm_bhld, pca_group_perm
+    def _resolve_topk(self, tp, cache: TokenSparseCache):
+        """Scalar or (B, H) budget from head / layer adaptation (token_sparse.py:1246-1258)."""
+        cfg = self.config
+        has_layer = cfg.adaptive_layers and cache.layer_t is not None
+        if cfg.adaptive_heads and tp.shape[1] > 1:
+            return _compute_adaptive_topk_token(tp, cfg.topk, layer_t=cache.layer_t if has_layer else None)
+        if has_layer:
+            return cfg.topk * (0.5 + cache.layer_t)
+        return cfg.topk
+
+    def _select(self, cache: TokenSparseCache, q_grp, k, lse, scale, perm=None):
+        """Group mass + selection of the anchor / update step.  ``q_grp`` is q itself when ``perm`` carries the
+        grouping (the mass kernel reads Q through it), else the queries in group order."""
+        cfg = self.config
+        if cfg.use_chunk_selector:
+            # the chunked selector of the reference exists to avoid the (B,H,M,L_K) score tensor; its result is
+            # the plain top-k of a fixed budget without sinks, lengths or head adaptation (token_sparse.py:1171-1178)
+            L_K = k.shape[2]
+            n = max(1, int(cfg.topk * L_K))
+            k_sel = min(((n + cfg.tile_n - 1) // cfg.tile_n) * cfg.tile_n, L_K)
+            gi = _chunked_online_topk(q_grp, k, lse, cfg.BLKQ, scale, k_sel, tile_n=cfg.tile_n,
+                                      chunk_size=cfg.chunk_selector_size, perm=perm)
+            return gi, None
+        mass = group_mass(q_grp, k, lse, group_rows=cfg.BLKQ, scale=scale, perm=perm, normalize=True)
+        return _select_topk_tokens(mass, self._resolve_topk(mass, cache), tile_n=cfg.tile_n,
+                                   selection_mode=cfg.selection_mode, topp=cfg.topp, sink_ranges=cfg.sink_ranges)
+
+    def forward(self, cache: TokenSparseCache, q, k, v, scale: Optional[float] = None, out_peers=None):
+        """Returns the (B,H,L,D) output, or None when ``out_peers`` was given and the call ended in the sparse
+        kernel (reuse step), whose epilogue then stored the rows into the owners' sequence shards."""
+        from mcsparse_b200.kernels.flash_mcsa.pca_group import invert_perm_bhld, pca_group_perm
         cfg = self.config
         B, H, L, D = q.shape
         if scale is None:
@@ -301,54 +413,85 @@ class TokenSparseBackend:
         mode = cache.mode
         if mode == 'full':
             return dense_attention_with_lse(q, k, v, scale)[0]
-        if mode in ('calibrate', 'full_calibrate'):
-            perm = None
-            if cfg.pca_reorder:
-                perm = pca_group_perm(q.reshape(B * H, L, D), C=cfg.BLKQ, pow_iters=cfg.pca_pow_iters, seed=cfg.pca_seed)
-                cache._perm_generation += 1
+        perm = cache._cached_perm
+        if cfg.pca_reorder and (mode in _SELECTION_RECOMPUTE_MODES or perm is None):
+            perm = pca_group_perm(q.reshape(B * H, L, D) if q.is_contiguous() else q.flatten(0, 1), C=cfg.BLKQ,
+                                  pow_iters=cfg.pca_pow_iters, seed=cfg.pca_seed)
+            cache._perm_generation += 1
             cache._cached_perm = perm
-            q_grp = q if perm is None else apply_perm_bhld(q, perm)
-            dense_grp, lse = dense_attention_with_lse(q_grp, k, v, scale)        # group (permuted) order
+        if not cfg.pca_reorder:
+            perm = None
+        if mode in ('calibrate', 'full_calibrate'):
+            cache._cached_len = (L, k.shape[2])
+            # dense pass on the regrouped queries, read through the permutation; output and LSE in group order
+            dense_grp, lse = dense_attention_with_lse(q, k, v, scale, perm=perm, group_order=perm is not None)
             cache._cached_lse = lse
-            mass = group_mass(q_grp, k, lse, group_rows=cfg.BLKQ, scale=scale)
-            gi, gl = _select_topk_tokens(mass, cfg.topk, tile_n=cfg.tile_n, sink_ranges=cfg.sink_ranges)
-            cache._cached_indices, cache._cached_lengths, cache._cached_len = gi, gl, (L, k.shape[2])
+            gi, gl = self._select(cache, q, k, lse, scale, perm=perm)
+            cache._cached_indices, cache._cached_lengths = gi, gl
             if cfg.bias_correction:
                 # residual = dense - sparse in one kernel pass (the reference runs the sparse kernel and then an
-                # elementwise subtraction, token_sparse.py:1209-1216); permuted-query order
-                cache._cached_residual = self._sparse(q_grp, k, v, gi, gl, scale, dense_grp, None, subtract=True)
+                # elementwise subtraction, token_sparse.py:1209-1216); both operands and the result in group order
+                cache._cached_residual = self._sparse(q, k, v, gi, gl, scale, dense_grp, perm, subtract=True,
+                                                      group_order=perm is not None)
                 cache._residual_perm_gen = cache._perm_generation
-            if perm is None:
-                return dense_grp
-            from mcsparse_b200.kernels.flash_mcsa.pca_group import invert_perm_bhld
-            return invert_perm_bhld(dense_grp, perm)
+            elif mode == 'calibrate':
+                # without bias correction a plain anchor step returns the sparse result (token_sparse.py:1290)
+                return self._sparse(q, k, v, gi, gl, scale, None, perm)
+            return dense_grp if perm is None else invert_perm_bhld(dense_grp, perm)
+        if mode == 'approx':
+            cache._cached_len = (L, k.shape[2])
+            gi = _approx_select(q, k, cfg, perm)
+            cache._cached_indices, cache._cached_lengths = gi, None
+            return self._sparse(q, k, v, gi, None, scale, None, perm)
         if mode == 'update':
-            perm = cache._cached_perm
-            q_grp = q if perm is None else apply_perm_bhld(q, perm)
-            mass = group_mass(q_grp, k, cache._cached_lse, group_rows=cfg.BLKQ, scale=scale)
-            cache._cached_indices, cache._cached_lengths = _select_topk_tokens(
-                mass, cfg.topk, tile_n=cfg.tile_n, sink_ranges=cfg.sink_ranges)
-        # reuse (and the attention of an update step): one fused kernel call
+            # new selection from the cached LSE (group order of the anchor step's permutation)
+            gi, gl = self._select(cache, q, k, cache._cached_lse, scale, perm=perm)
+            cache._cached_indices, cache._cached_lengths = gi, gl
+            if cfg.bias_correction:
+                # the residual belongs to the selection: renew it against a fresh dense pass and return the dense
+                # output (token_sparse.py:1333-1341)
+                dense_grp, _ = dense_attention_with_lse(q, k, v, scale, perm=perm, group_order=perm is not None)
+                cache._cached_residual = self._sparse(q, k, v, gi, gl, scale, dense_grp, perm, subtract=True,
+                                                      group_order=perm is not None)
+                cache._residual_perm_gen = cache._perm_generation
+                return dense_grp if perm is None else invert_perm_bhld(dense_grp, perm)
+            return self._sparse(q, k, v, gi, gl, scale, None, perm)
+        # reuse: one fused kernel call
         residual = cache.residual_if_valid() if cfg.bias_correction else None
-        return self._sparse(q, k, v, cache._cached_indices, cache._cached_lengths, scale, residual, cache._cached_perm)
+        return self._sparse(q, k, v, cache._cached_indices, cache._cached_lengths, scale, residual, perm,
+                            out_peers=out_peers)
 
 
 class TokenSparseContext:
-    """All layers of a model: one cache per layer, one step clock (token_sparse.py:1461-1845)."""
+    """All layers of a model: one cache per layer, one step clock (token_sparse.py:1461-1845).  Without
+    ``num_layers`` the caches are created as layers show up (``cache(li)``)."""
 
-    def __init__(self, config: TokenSparseConfig, num_layers: int):
+    def __init__(self, config: TokenSparseConfig, num_layers: Optional[int] = None):
         self.config = config
         self.backend = TokenSparseBackend(config)
-        self.caches = [TokenSparseCache(config) for _ in range(num_layers)]
+        self._nl = num_layers
+        self.caches: List[TokenSparseCache] = []
+        for i in range(num_layers or 0):
+            self.cache(i)
 
-    def forward(self, li: int, q, k, v, scale: Optional[float] = None):
+    def cache(self, li: int) -> TokenSparseCache:
+        while len(self.caches) <= li:
+            i = len(self.caches)
+            t = i / max(self._nl - 1, 1) if (self._nl and self.config.adaptive_layers) else None
+            self.caches.append(TokenSparseCache(self.config, i, t))
+        return self.caches[li]
+
+    def forward(self, li: int, q, k, v, scale: Optional[float] = None, out_peers=None):
         if li in self.config.full_layers:
             return dense_attention_with_lse(q, k, v, scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))[0]
-        return self.backend.forward(self.caches[li], q, k, v, scale)
+        return self.backend.forward(self.cache(li), q, k, v, scale, out_peers=out_peers)
 
     def step(self) -> None:
         for c in self.caches:
             c.step()
+        # once per denoising step, without synchronising: did any kernel report an expired wait?
+        if self.caches and torch.cuda.is_available():
+            _lib.poll_status(torch.cuda.current_device(), "TokenSparseContext.step")
 
     def reset(self) -> None:
         for c in self.caches:

@@ -89,11 +89,15 @@ def clustered_qkv(shape: VideoShape, heads: Optional[int] = None, seed: int = 0,
 
 
 def residual_like(shape: VideoShape, heads: Optional[int] = None, seed: int = 1, device="cpu",
-                  dtype=torch.bfloat16) -> torch.Tensor:
-    """Cached dense-minus-sparse residual stand-in: (1, H, L, D) ~ N(0, 0.01) (sigma 0.1)."""
+                  dtype=torch.bfloat16, head_offset: int = 0) -> torch.Tensor:
+    """Cached dense-minus-sparse residual stand-in: (1, H, L, D) ~ N(0, 0.01) (sigma 0.1).  Generated head by
+    head from per-head seeds, so any head subset reproduces the values of the full tensor."""
     H = heads or shape.heads
-    g = torch.Generator(device=device).manual_seed(seed * 7 + 3)
-    return (0.1 * torch.randn(1, H, shape.seq_len, shape.head_dim, generator=g, device=device)).to(dtype)
+    out = torch.empty(1, H, shape.seq_len, shape.head_dim, dtype=dtype, device=device)
+    for h in range(H):
+        g = torch.Generator(device=device).manual_seed(seed * 7 + 3 + (head_offset + h) * 104729)
+        out[0, h] = (0.1 * torch.randn(shape.seq_len, shape.head_dim, generator=g, device=device)).to(dtype)
+    return out
 
 
 def random_sorted_indices(B, H, M, gather_len, Sk, seed=0, n_sink=N_SINK, device="cpu") -> torch.Tensor:

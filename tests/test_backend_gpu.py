@@ -67,3 +67,56 @@ def test_topmass_indices_helper(cuda_device):
     # selection from the kernel's own fp32 mass is exact; against the fp64 oracle mass near-ties may swap
     agree = (gi == ref).float().mean().item()
     assert agree > 0.97, agree
+
+
+def test_update_step_refreshes_residual(cuda_device):
+    """An update step re-selects the tokens from the cached LSE; with bias correction it must also renew the
+    residual against a fresh dense pass and return the dense output (reference token_sparse.py:1333-1341), so
+    that the next reuse step adds a residual that belongs to the selection it uses."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    B, H, L, D = 1, 2, 1500, 128
+    cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], update_steps=[1], sink_ranges=[(0, 4)], bias_correction=True,
+                            pca_reorder=True, pca_pow_iters=4)
+    ctx = TokenSparseContext(cfg, num_layers=1)
+    dev = cuda_device
+    q, k, v = _qkv(B, H, L, D, 1)
+    ctx.forward(0, q.to(dev), k.to(dev), v.to(dev))
+    cache = ctx.caches[0]
+    gi0, res0, gen0 = cache._cached_indices.clone(), cache._cached_residual.clone(), cache._perm_generation
+    ctx.step()
+    assert cache.mode == "update"
+    q2, k2, v2 = _qkv(B, H, L, D, 2)
+    out1 = ctx.forward(0, q2.to(dev), k2.to(dev), v2.to(dev)).float().cpu()
+    dense2, _ = dense_attn_ref(q2.transpose(1, 2), k2.transpose(1, 2), v2.transpose(1, 2))
+    mx, mr = error_metrics(out1.transpose(1, 2), dense2)
+    assert mx < 2e-2 and mr < 1e-2, (mx, mr)                       # the update step returns the dense result
+    assert cache._perm_generation == gen0                          # the permutation is kept
+    assert not torch.equal(cache._cached_indices, gi0)             # the selection is new
+    assert not torch.equal(cache._cached_residual, res0)           # and so is the residual
+    # the new residual is dense - sparse(new selection) in group order: a reuse step on the same tensors gives dense
+    ctx.step()
+    assert cache.mode == "reuse"
+    out2 = ctx.forward(0, q2.to(dev), k2.to(dev), v2.to(dev)).float().cpu()
+    mx, mr = error_metrics(out2.transpose(1, 2), dense2)
+    assert mx < 3e-2 and mr < 1.5e-2, (mx, mr)
+    gi, gl, perm = cache._cached_indices.cpu(), cache._cached_lengths, cache._cached_perm.cpu()
+    sparse2, _ = gather_attn_ref(q2.transpose(1, 2), k2.transpose(1, 2), v2.transpose(1, 2), gi,
+                                 gl=None if gl is None else gl.cpu(), perm=perm)
+    want = torch.stack([(dense2 - sparse2)[0, perm[h], h] for h in range(H)]).unsqueeze(0)      # (1,H,L,D) group order
+    assert float((cache._cached_residual.float().cpu() - want).abs().max()) < 2e-2
+
+
+def test_plain_calibrate_returns_sparse_output(cuda_device):
+    """Without bias correction an anchor step returns the sparse result (reference token_sparse.py:1290)."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    B, H, L, D = 1, 2, 1024, 128
+    cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], bias_correction=False, pca_reorder=False)
+    ctx = TokenSparseContext(cfg, num_layers=1)
+    q, k, v = _qkv(B, H, L, D, 3)
+    dev = cuda_device
+    out = ctx.forward(0, q.to(dev), k.to(dev), v.to(dev)).float().cpu()
+    cache = ctx.caches[0]
+    assert cache._cached_residual is None and cache._cached_lengths is None
+    ref, _ = gather_attn_ref(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), cache._cached_indices.cpu())
+    mx, mr = error_metrics(out.transpose(1, 2), ref)
+    assert mx < 2e-2 and mr < 1e-2, (mx, mr)

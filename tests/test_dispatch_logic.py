@@ -19,6 +19,11 @@ def test_mode_schedule():
             cache._cached_indices = object()
         cache.step()
     assert seen == ["full_calibrate", "reuse", "full", "update", "reuse", "calibrate", "reuse"]
+    c2 = TokenSparseConfig(topk=0.1, calibrate_steps=[0], approx_steps=[2])
+    cache = TokenSparseCache(c2)
+    cache._cached_indices = object()
+    cache._step_count = 2
+    assert cache.mode == "approx"
     assert TokenSparseCache(TokenSparseConfig()).mode == "calibrate"        # no cache -> calibrate
 
 
@@ -31,8 +36,13 @@ def test_config_guards():
         TokenSparseConfig(sink_ranges=[(4, 4)])
     with pytest.raises(AssertionError):
         TokenSparseConfig(pca_reorder=True, share_lse=True)
+    with pytest.raises(AssertionError):
+        TokenSparseConfig(selection_mode="topp")                      # topp modes need topp
+    assert TokenSparseConfig(selection_mode="topk_topp", topp=0.9).topp == 0.9
     with pytest.raises(NotImplementedError):
-        TokenSparseConfig(selection_mode="topp", topp=0.9)
+        TokenSparseConfig(cal_downsample=2)
+    with pytest.raises(NotImplementedError):
+        TokenSparseConfig(pca_proj_dim=32)
 
 
 def test_residual_dropped_when_permutation_is_newer():
@@ -81,6 +91,9 @@ class FakeTensor:
     def transpose(self, a, b):
         return self._t.transpose(a, b)
 
+    def contiguous(self):
+        return self
+
 
 def test_dispatch_counters_and_layer_clock():
     ctx = FakeCtx(3)
@@ -128,3 +141,145 @@ def test_dispatch_guards():
         d(t, t, t)                         # a second sparse layer without a new step: numbering would drift
     tsd.reset_mcsa_token_state()
     assert tsd.get_mcsa_token_stats()["dispatch_calls"] == 0 and ctx.resets >= 1
+
+
+def test_schedule_translation():
+    """dense_steps / dense_layers / calibrate_every -> step and layer sets (reference :561-632)."""
+    s = tsd.build_schedule(num_steps=50, dense_steps=10, dense_layers="0-1", calibrate_every=10, calibrate_steps=(9, 25))
+    assert s == {"full_steps": list(range(10)), "full_layers": [0, 1], "calibrate_steps": [9, 25], "free_calibrate_step": 9}
+    s = tsd.build_schedule(num_steps=50, dense_steps=10, dense_layers="0,3-4", calibrate_every=10)
+    assert s["calibrate_steps"] == [9, 19, 29, 39] and s["full_layers"] == [0, 3, 4]       # 49 = last step: dropped
+    s = tsd.build_schedule(num_steps=20, dense_steps=0, dense_layers="", calibrate_every=7)
+    assert s["full_steps"] is None and s["calibrate_steps"] == [0, 7, 14] and s["free_calibrate_step"] is None
+    s = tsd.build_schedule(num_steps=1, dense_steps=0, dense_layers="", calibrate_every=5)
+    assert s["calibrate_steps"] == [0]
+    for bad in (dict(num_steps=0, dense_steps=0), dict(num_steps=5, dense_steps=-1), dict(num_steps=5, dense_steps=0, calibrate_every=0)):
+        kw = dict(dense_layers="", calibrate_every=10)
+        kw.update(bad)
+        with pytest.raises(ValueError):
+            tsd.build_schedule(**kw)
+    with pytest.raises(ValueError):
+        tsd.build_schedule(num_steps=5, dense_steps=0, dense_layers="", calibrate_every=1, calibrate_steps=())
+    tsd.validate_schedule(num_steps=10, calibrate_steps=[0, 5], update_steps=[3], approx_steps=None)
+    with pytest.raises(ValueError):
+        tsd.validate_schedule(num_steps=10, calibrate_steps=[0, 5], update_steps=[5], approx_steps=None)
+    with pytest.raises(ValueError):
+        tsd.validate_schedule(num_steps=10, calibrate_steps=[0], update_steps=[12], approx_steps=None)
+    assert tsd.effective_density(sink_tokens=300, seq_len=38011, topk=0.25) == (9600 + 300) / 38011
+    assert tsd.effective_density(sink_tokens=0, seq_len=0, topk=0.25) == 0.0
+
+
+def test_eligibility_table():
+    base = dict(ndim=4, is_cuda=True, dtype_ok=True, shapes_match=True, head_dim=128, seq_len_q=8192, seq_len_k=8192,
+                has_attn_mask=False, is_causal=False, dropout_p=0.0, enable_gqa=False, scale=None, min_seq_len=4096,
+                sparse_seq_len=None, has_parallel_config=False, sink_tokens=0)
+    assert tsd.check_eligibility(**base) == (True, "", "")
+    for change in (dict(has_parallel_config=True), dict(has_attn_mask=True), dict(is_causal=True), dict(dropout_p=0.1),
+                   dict(enable_gqa=True), dict(ndim=3), dict(is_cuda=False), dict(dtype_ok=False), dict(shapes_match=False),
+                   dict(seq_len_k=4096), dict(head_dim=96), dict(seq_len_q=301, seq_len_k=301), dict(sparse_seq_len=16384)):
+        ok, reason, severity = tsd.check_eligibility(**{**base, **change})
+        assert not ok and reason and severity == "fallback", change
+    ok, _, severity = tsd.check_eligibility(**{**base, "sink_tokens": 8192})
+    assert not ok and severity == "raise"
+
+
+class _Cfg:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def test_parallel_config_falls_back_and_sink_splice():
+    ctx = FakeCtx(1)
+    seen = []
+
+    def original(q, k, v, *a, **kw):
+        seen.append((tuple(q.shape), kw.get("parallel_config")))
+        return torch.ones(q.shape, dtype=torch.bfloat16)
+
+    d = tsd.make_mcsa_token_dispatch(original, num_layers=1, topk=0.15, sink_tokens=8, min_seq_len=1024, context=ctx)
+    t = FakeTensor((1, 2048, 2, 128))
+    tsd.mcsa_token_begin_forward()
+    pc = _Cfg(context_parallel_config=_Cfg(ulysses_degree=2, ring_degree=1))
+    out = d(t, t, t, parallel_config=pc)                      # sequence shard: never sparsified here
+    assert seen[-1] == ((1, 2048, 2, 128), pc) and tsd.get_mcsa_token_stats()["fallback_calls"] == 1
+    assert ctx.forwards == []
+    # eligible call: sparse path, then the first 8 query rows are recomputed densely and spliced in
+    q = torch.zeros(1, 2048, 2, 128, dtype=torch.bfloat16)
+    q.is_cuda_fake = True
+
+    class Cuda(torch.Tensor):
+        is_cuda = True
+    qc = q.as_subclass(Cuda)
+    out = d(qc, qc, qc)
+    s = tsd.get_mcsa_token_stats()
+    assert s["kernel_calls"] == 1 and s["splice_calls"] == 1 and s["sink_tokens"] == 8
+    assert seen[-1][0] == (1, 8, 2, 128)
+    assert tuple(out.shape) == (1, 2048, 2, 128) and bool((out[:, :8] == 1).all()) and bool((out[:, 8:] == 0).all())
+    with pytest.raises(ValueError):
+        tsd.make_mcsa_token_dispatch(original, num_layers=1, sink_tokens=0, allow_no_sink=False, context=FakeCtx(1))
+    with pytest.raises(ValueError):
+        tsd.make_mcsa_token_dispatch(original, num_layers=1, sink_tokens=4, use_chunk_selector=True, context=FakeCtx(1))
+    with pytest.raises(ValueError):
+        tsd.make_mcsa_token_dispatch(original, num_layers=1, cache_offload="residual", bias_correction=False, context=FakeCtx(1))
+
+
+def test_kernel_problem_is_counted_and_served_densely():
+    from mcsparse_b200 import _lib
+
+    class Failing(FakeCtx):
+        def forward(self, li, q, k, v, scale):
+            raise _lib.KernelStatusError("kernel status 30")
+
+    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=Failing(1))
+    t = FakeTensor((1, 2048, 2, 128))
+    tsd.mcsa_token_begin_forward()
+    assert d(t, t, t) == "dense"
+    s = tsd.get_mcsa_token_stats()
+    assert s["kernel_error_calls"] == 1 and s["fallback_calls"] == 1 and s["kernel_calls"] == 0
+    assert s["dispatch_calls"] == s["fallback_calls"] + s["dense_guard_calls"] + s["kernel_calls"]
+
+
+def test_ticks_per_step():
+    ctx = FakeCtx(1)
+    tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx, ticks_per_step=2)
+    for _ in range(6):
+        tsd.mcsa_token_begin_forward()
+    assert ctx.steps == 2 and tsd.get_mcsa_token_stats()["steps_ticked"] == 3
+
+
+def test_with_ulysses_sparse_truth_table():
+    """The branches of the reference wrapper (context_parallel.py:183-229) with fake tensors and configurations."""
+    from mcsparse_b200.h3 import context_parallel as cp
+    calls = []
+
+    def inner(q, k, v, *a, **kw):
+        calls.append(("kernel", kw.get("parallel_config")))
+        return "sparse"
+
+    def original(q, k, v, *a, **kw):
+        calls.append(("original", kw.get("parallel_config")))
+        return "dense"
+
+    cp.reset_cp_stats()
+    d = cp.with_ulysses_sparse(original, kind="mcsa_token", _inner_dispatch=inner, topk=0.15)
+    t = FakeTensor((1, 2048, 2, 128))
+    assert d(t, t, t) == "sparse" and cp.get_cp_stats() == {"cp_calls": 0, "local_calls": 1}
+    assert d(t, t, t, parallel_config=_Cfg(context_parallel_config=None)) == "sparse"
+    assert d(t, t, t, parallel_config=_Cfg(context_parallel_config=_Cfg(ulysses_degree=1, ring_degree=1))) == "sparse"
+    assert cp.get_cp_stats() == {"cp_calls": 0, "local_calls": 3}
+    assert all(c == ("kernel", None) for c in calls)            # past the wrapper the kernel never sees a parallel_config
+    # unsupported arguments go to the original dispatch untouched, uncounted
+    pc = _Cfg(context_parallel_config=_Cfg(ulysses_degree=2, ring_degree=1))
+    for kw in (dict(attn_mask=object()), dict(is_causal=True), dict(dropout_p=0.1), dict(enable_gqa=True), dict(scale=0.5)):
+        assert d(t, t, t, parallel_config=pc, **kw) == "dense"
+    assert d(FakeTensor((1, 2048, 2, 128), cuda=False), t, t) == "dense"
+    assert d(t, FakeTensor((1, 1024, 2, 128)), t) == "dense"
+    assert calls[-1] == ("original", None) and cp.get_cp_stats() == {"cp_calls": 0, "local_calls": 3}
+    with pytest.raises(ValueError, match="ring_degree"):
+        d(t, t, t, parallel_config=_Cfg(context_parallel_config=_Cfg(ulysses_degree=2, ring_degree=2)))
+    with pytest.raises(ValueError):
+        cp.with_ulysses_sparse(original, kind="block_sparse")
+    with pytest.raises(ValueError, match="LSE"):
+        d.forward_op(None, t, t, t, return_lse=True)
+    cp.reset_cp_stats()
+    assert cp.get_cp_stats() == {"cp_calls": 0, "local_calls": 0}

@@ -81,3 +81,18 @@ def test_short_sequence_is_identity(cuda_device):
     from mcsparse_b200.kernels.flash_mcsa.pca_group import pca_group_perm
     x = torch.randn(2, 100, 128).to(torch.bfloat16).to(cuda_device)
     assert torch.equal(pca_group_perm(x, C=128).cpu(), torch.arange(100).expand(2, 100))
+
+
+@pytest.mark.parametrize("N,C", [(8, 2), (4, 3), (37, 5), (64, 4)])
+def test_tiny_groups(cuda_device, N, C):
+    """Groups smaller than the projection kernel's row batch (8 slots): nodes of 1 to 7 tokens."""
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import pca_group_perm, pddp_start_vectors
+    BH, D = 2, 64
+    x = _clustered(BH, N, D, 100 + N)
+    sv = pddp_start_vectors(BH, N, C, D, seed=0)
+    perm, proj, orders = pca_group_perm(x.to(cuda_device), C=C, pow_iters=4, start_vectors=sv, return_debug=True)
+    perm, proj, orders = perm.cpu(), proj.cpu(), orders.cpu().long()
+    assert torch.equal(perm.sort(dim=1).values, torch.arange(N).expand(BH, N))
+    for li, nodes in enumerate(level_ranges(N, C)):
+        assert torch.equal(resort_from_projections(orders[li], proj[li], nodes), orders[li + 1]), f"level {li}"
+    assert torch.equal(orders[-1], perm)

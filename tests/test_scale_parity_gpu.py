@@ -1,0 +1,267 @@
+"""GPU parity at the sizes of the benchmark configurations.
+
+The attention kernel is persistent (one CTA per SM walks its work items round-robin), so only inputs with
+several times more work items than SMs exercise its steady state: the Q double buffer and its phase bits,
+the K/V ring running across item boundaries, the epilogue of item i under the main loop of item i+1.  Every
+case here has at least 3 items per SM of a 148-SM part and is compared with the CPU oracle (whole heads) or
+with an oracle evaluated on a sample of rows spread over all groups (dense attention, group mass), through
+the C ABI.  Indices are the benchmark's own: 4 sink tokens plus the top tokens by exact fp32 group mass.
+"""
+
+import dataclasses
+import math
+
+import pytest
+import torch
+
+from oracle.gather_attn import error_metrics, gather_attn_fp8_ref, gather_attn_ref
+from oracle.pddp import level_ranges, resort_from_projections
+from oracle.select import select_topk_ref
+
+pytestmark = pytest.mark.gpu
+
+BF16_MAX_ABS, BF16_MEAN_REL = 2e-2, 1e-2
+FP8_MAX_ABS, FP8_MEAN_REL = 6e-2, 3e-2
+
+
+def _cpu(*ts):
+    return tuple(t.cpu() for t in ts)
+
+
+def _c2_case(dev, heads=2):
+    """Two heads of the bf16 video-DiT configuration with a Fast PDDP permutation, top-mass indices built in
+    the permuted group order and a residual: 512 work items."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import apply_perm, pca_group_perm
+    shape = dataclasses.replace(synth.C2, heads=heads)
+    q, k, v = synth.clustered_qkv(shape, heads=heads, device=dev)
+    x = q[0].transpose(0, 1)                                   # (H, L, D) view
+    perm = pca_group_perm(x, C=128, pow_iters=8, seed=0)
+    q_grp = apply_perm(x.contiguous(), perm).transpose(0, 1).unsqueeze(0)     # (1, L, H, D) in group order
+    gi = synth.topmass_indices(q_grp, k, shape)
+    res = synth.residual_like(shape, heads=heads, device=dev)
+    return shape, q, k, v, perm, gi, res
+
+
+def test_c2_two_heads_reuse_step(cuda_device):
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    shape, q, k, v, perm, gi, res = _c2_case(cuda_device)
+    assert gi.shape == (1, 2, 256, 2048) and bool((gi[..., :4] == torch.arange(4, device=gi.device)).all())
+    assert bool((gi[..., 1:] > gi[..., :-1]).all())
+    out, lse = flash_attn_gather_kv_func(q, k, v, gi, return_lse=True, residual=res, perm=perm)
+    torch.cuda.synchronize()
+    ref, ref_lse = gather_attn_ref(*_cpu(q, k, v, gi), residual=res.cpu(), perm=perm.cpu())
+    mx, mr = error_metrics(out.float().cpu(), ref)
+    assert mx < BF16_MAX_ABS and mr < BF16_MEAN_REL, (mx, mr)
+    assert float((lse.cpu() - ref_lse).abs().max()) < 2e-2
+    # the same call twice gives the same bits (no dependence on CTA scheduling)
+    out2, _ = flash_attn_gather_kv_func(q, k, v, gi, residual=res, perm=perm)
+    assert torch.equal(out, out2)
+
+
+def test_c2_ragged_tile_counts_many_items(cuda_device):
+    """Four heads of 16,456 tokens (last group 72 rows), random tile counts 1..3 per group, D = 64 and 128:
+    516 items whose lengths differ, so CTAs drift apart and every hand-over happens at a different tile."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    dev = cuda_device
+    for D in (128, 64):
+        B, H, Sq, Sk, KS = 1, 4, 16456, 1024, 384
+        g = torch.Generator().manual_seed(100 + D)
+        q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(B, Sk, H, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Sk, H, D, generator=g).to(torch.bfloat16)
+        M = math.ceil(Sq / 128)
+        gi = synth.random_sorted_indices(B, H, M, KS, Sk, seed=D)
+        gl = torch.randint(1, 4, (B, H, M), generator=g, dtype=torch.int32)
+        res = (0.1 * torch.randn(B, H, Sq, D, generator=g)).to(torch.bfloat16)
+        perm = torch.stack([torch.randperm(Sq, generator=g) for _ in range(B * H)])
+        out, lse = flash_attn_gather_kv_func(q.to(dev), k.to(dev), v.to(dev), gi.to(dev), return_lse=True,
+                                             gather_kv_lengths=gl.to(dev), residual=res.to(dev), perm=perm.to(dev))
+        torch.cuda.synchronize()
+        ref, ref_lse = gather_attn_ref(q, k, v, gi, gl=gl, residual=res, perm=perm)
+        mx, mr = error_metrics(out.float().cpu(), ref)
+        assert mx < BF16_MAX_ABS and mr < BF16_MEAN_REL, (D, mx, mr)
+        assert float((lse.cpu() - ref_lse).abs().max()) < 2e-2
+
+
+def _sample_rows(L, per_group, seed):
+    g = torch.Generator().manual_seed(seed)
+    M = math.ceil(L / 128)
+    rows = []
+    for m in range(M):
+        n = min(128, L - m * 128)
+        rows.append(m * 128 + torch.randperm(n, generator=g)[:per_group])
+    return torch.cat(rows)
+
+
+def test_c2_dense_pass_and_residual_construction(cuda_device):
+    """Anchor-step attention at L = 32,760 on two heads (512 items of 256 key tiles each): output and LSE of
+    the dense mode on rows sampled from every group, then ``dense - sparse`` in one pass."""
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    from mcsparse_b200.kernels.flash_mcsa.ops.full_attn import full_attention_with_lse
+    shape, q, k, v, perm, gi, res = _c2_case(cuda_device)
+    qh, kh, vh = (t.transpose(1, 2) for t in (q, k, v))         # (1, H, L, D) views of (1, L, H, D) storage
+    dense, lse = full_attention_with_lse(qh, kh, vh)
+    torch.cuda.synchronize()
+    rows = _sample_rows(shape.seq_len, 6, seed=1)
+    qc, kc, vc = _cpu(q, k, v)
+    scale = 1.0 / math.sqrt(shape.head_dim)
+    for h in range(2):
+        s = (qc[0, rows, h].float() @ kc[0, :, h].float().T) * scale
+        ref_o = torch.softmax(s, -1) @ vc[0, :, h].float()
+        mx, mr = error_metrics(dense[0, h].float().cpu()[rows], ref_o)
+        assert mx < BF16_MAX_ABS and mr < BF16_MEAN_REL, (h, mx, mr)
+        assert float((lse[0, h].cpu()[rows] - torch.logsumexp(s, -1)).abs().max()) < 2e-3
+    # residual construction: out = dense - sparse (dense given in group order, like the residual)
+    dense_grp = torch.stack([dense[0, h][perm[h]] for h in range(2)]).unsqueeze(0)
+    r, _ = flash_attn_gather_kv_func(q, k, v, gi, residual=dense_grp, perm=perm, residual_minus_attention=True)
+    torch.cuda.synchronize()
+    sparse_ref, _ = gather_attn_ref(qc, kc, vc, gi.cpu())       # original order
+    ref_r = dense.float().cpu().transpose(1, 2) - sparse_ref
+    mx, mr = error_metrics(r.float().cpu(), ref_r)
+    assert mx < BF16_MAX_ABS, mx
+    assert float((r.float().cpu() - ref_r).abs().mean()) < 2e-3
+
+
+def test_c3_fp8_one_head(cuda_device):
+    """One head of the FP8 long-video configuration: 768 groups x top-k 4096 of L = 98,280, per-head e4m3
+    quantisation (scale = amax / 448), bf16 residual."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_fp8_func
+    dev = cuda_device
+    shape = dataclasses.replace(synth.C3, heads=1)
+    q, k, v = synth.clustered_qkv(shape, heads=1, device=dev)
+    gi = synth.topmass_indices(q, k, shape)
+    assert gi.shape == (1, 1, 768, 4096)
+    q8, sq = synth.quantize_e4m3_per_head(q)
+    k8, sk = synth.quantize_e4m3_per_head(k)
+    v8, sv = synth.quantize_e4m3_per_head(v)
+    D, M = shape.head_dim, shape.n_groups
+    scale_qk = (sq * sk * (D ** -0.5) * math.log2(math.e)).view(1, 1, 1).expand(1, 1, M).contiguous().float()
+    res = synth.residual_like(shape, heads=1, device=dev)
+    out, lse = flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, scale_qk, sv.float(), return_lse=True, residual=res)
+    torch.cuda.synchronize()
+    ref, ref_lse = gather_attn_fp8_ref(*_cpu(q8, k8, v8, gi, scale_qk, sv), residual=res.cpu())
+    mx, mr = error_metrics(out.float().cpu(), ref)
+    assert mx < FP8_MAX_ABS and mr < FP8_MEAN_REL, (mx, mr)
+    assert float((lse.cpu() - ref_lse).abs().max()) < 5e-2
+
+
+@pytest.mark.parametrize("world", [8])
+def test_fused_ulysses_emulated_many_items(cuda_device, world):
+    """The fused Ulysses path with eight emulated ranks, 384 work items per rank (one local head of 49,152
+    tokens): scatter into the peers' buffers, attention whose epilogue stores each row into the owner's
+    sequence shard, against the oracle on the unsharded tensors."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.h3.context_parallel import PeerBuffers, UlyssesFusedAttention
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    dev = cuda_device
+    L, H, D, topk = 49152, world, 128, 1024
+    Ls, Hl = L // world, H // world
+    g = torch.Generator().manual_seed(17)
+    q, k, v = (torch.randn(1, L, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    res = (0.1 * torch.randn(1, H, L, D, generator=g)).to(torch.bfloat16)
+    gi = torch.cat([synth.random_sorted_indices(1, 1, L // 128, topk, L, seed=h) for h in range(H)], dim=1)
+    perm = torch.stack([torch.randperm(L, generator=g) for _ in range(H)])
+    qd, kd, vd, resd, gid, permd = (t.to(dev) for t in (q, k, v, res, gi, perm))
+    bufs = PeerBuffers.emulated(world, L, Ls, H, Hl, 1, D, torch.bfloat16, dev)
+    ranks = [UlyssesFusedAttention(None, L, H, D, torch.bfloat16, dev, chunks=1, buffers=bufs[r], rank=r, world=world)
+             for r in range(world)]
+    shard = lambda t, r: t[:, r * Ls:(r + 1) * Ls].contiguous()
+    for r, u in enumerate(ranks):
+        u.scatter_chunk(shard(qd, r), shard(kd, r), shard(vd, r), 0)
+    torch.cuda.synchronize()
+    for r, u in enumerate(ranks):
+        rc = u.buf.recv[0]
+        for i, t in enumerate((qd, kd, vd)):
+            assert torch.equal(rc[i], t[0, :, r * Hl:(r + 1) * Hl]), (r, i)
+        flash_attn_gather_kv_func(rc[0].unsqueeze(0), rc[1].unsqueeze(0), rc[2].unsqueeze(0), gid[:, r * Hl:(r + 1) * Hl],
+                                  residual=resd[:, r * Hl:(r + 1) * Hl], perm=permd[r * Hl:(r + 1) * Hl].contiguous(),
+                                  out_peers=u.out_peers(0))
+    torch.cuda.synchronize()
+    out = torch.cat([bufs[r].out for r in range(world)], dim=0).unsqueeze(0).float().cpu()
+    ref, _ = gather_attn_ref(q, k, v, gi, residual=res, perm=perm)
+    mx, mr = error_metrics(out, ref)
+    assert mx < BF16_MAX_ABS and mr < BF16_MEAN_REL, (mx, mr)
+
+
+def test_c4_anchor_metadata_one_head(cuda_device):
+    """Anchor-step metadata at L = 32,760 on one head: group mass against an fp64 oracle on sampled groups,
+    selection bit-exact from the kernel's own fp32 mass (k = 2048 with 4 sinks), Fast PDDP in its two stages
+    (projections within tolerance on sampled nodes, order exactly the stable sort of the kernel's projections)."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import pca_group_perm, pddp_start_vectors
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import dense_attention_with_lse, group_mass, select_topk_with_sinks
+    dev = cuda_device
+    shape = dataclasses.replace(synth.C2, heads=1)
+    q, k, _ = synth.clustered_qkv(shape, heads=1, device=dev)
+    qh, kh = q.transpose(1, 2), k.transpose(1, 2)
+    L, D = shape.seq_len, shape.head_dim
+    scale = 1.0 / math.sqrt(D)
+    _, lse = dense_attention_with_lse(qh, kh, kh, scale)
+    mass = group_mass(qh, kh, lse, scale=scale)
+    gi = select_topk_with_sinks(mass, shape.topk, [(0, 4)])
+    torch.cuda.synchronize()
+    qc, kc = q[0, :, 0].cpu().double(), k[0, :, 0].cpu().double()
+    lse_c, mass_c = lse[0, 0].cpu().double(), mass[0, 0].cpu()
+    for m in (0, 1, 77, 128, 200, 254, 255):
+        rows = slice(m * 128, min((m + 1) * 128, L))
+        s = qc[rows] @ kc.T * scale
+        # the kernel's own LSE (fp32) against the exact one, then the mass given the kernel's LSE
+        assert float((torch.logsumexp(s, -1) - lse_c[rows]).abs().max()) < 2e-3
+        ref = torch.exp(s - lse_c[rows, None]).sum(0)
+        assert float((mass_c[m].double() - ref).abs().max() / ref.max()) < 2e-3, m
+        assert abs(float(mass_c[m].double().sum()) - (rows.stop - rows.start)) < 0.5
+    # selection: a pure function of the fp32 mass the kernel produced
+    assert torch.equal(gi[0, 0].cpu(), select_topk_ref(mass_c, shape.topk, [0, 1, 2, 3]))
+    # Fast PDDP, 8 levels
+    _pddp_two_stage(dev, q[0].transpose(0, 1), 128, 8)
+
+
+def _pddp_two_stage(dev, x, C, iters, sample_nodes=6):
+    from mcsparse_b200.kernels.flash_mcsa.pca_group import pca_group_perm, pddp_start_vectors
+    from oracle.pddp import start_vectors
+    BH, N, D = x.shape
+    sv = pddp_start_vectors(BH, N, C, D, seed=0)
+    perm, proj, orders = pca_group_perm(x, C=C, pow_iters=iters, start_vectors=sv, return_debug=True)
+    torch.cuda.synchronize()
+    perm, proj, orders = perm.cpu(), proj.cpu(), orders.cpu().long()
+    levels = level_ranges(N, C)
+    assert proj.shape[0] == len(levels)
+    assert torch.equal(orders[-1], perm)
+    assert torch.equal(perm.sort(dim=1).values, torch.arange(N).expand(BH, N))
+    xf = x.float().cpu()
+    v0 = start_vectors(BH, N, C, D, 0)
+    g = torch.Generator().manual_seed(N)
+    for li, nodes in enumerate(levels):
+        before, after = orders[li], orders[li + 1]
+        assert torch.equal(resort_from_projections(before, proj[li], nodes), after), f"level {li}"
+        picks = torch.randperm(len(nodes), generator=g)[:sample_nodes].tolist()
+        for b in range(BH):
+            for ni in picks:
+                s, e = nodes[ni]
+                X = xf[b, before[b, s:e]]
+                ssum = X.sum(0)
+                G = X.T @ X - torch.outer(ssum, ssum) / (e - s)
+                v = v0[li][b * len(nodes) + ni].clone()
+                v = v / v.norm().clamp(min=1e-12)
+                for _ in range(iters):
+                    v = G @ v
+                    v = v / v.norm().clamp(min=1e-12)
+                a = X @ v
+                err = (a - proj[li][b, s:e]).abs().max() / a.abs().max().clamp(min=1e-6)
+                assert err < 2e-3, (li, b, ni, float(err))
+    return len(levels)
+
+
+def test_pddp_long_video_ten_levels(cuda_device):
+    """N = 98,280 (768 blocks, not a power of two): ten levels, and the 256 single-block nodes of the last
+    level are processed again like every other interval (pca_group.py:187-188)."""
+    from mcsparse_b200 import synth
+    dev = cuda_device
+    shape = dataclasses.replace(synth.C3, heads=1)
+    q, _, _ = synth.clustered_qkv(shape, heads=1, device=dev)
+    levels = level_ranges(shape.seq_len, 128)
+    assert len(levels) == 10 and sum(1 for s, e in levels[-1] if e - s <= 128) >= 256
+    assert _pddp_two_stage(dev, q[0].transpose(0, 1), 128, 8, sample_nodes=4) == 10
