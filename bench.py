@@ -805,7 +805,7 @@ def main():
     ap.add_argument("--no-single", action="store_true", help="N > 1: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
-    ap.add_argument("--e2e-chunk", type=int, default=4, help="heads per chunk of the pipelined end-to-end step (one GPU)")
+    ap.add_argument("--e2e-chunk", type=int, default=2, help="heads per chunk of the pipelined end-to-end step (one GPU)")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
                          "attn_fp8: the e4m3 variant at the long-video shape (1 GPU)")

@@ -106,7 +106,8 @@ struct Smem {
   static constexpr int kBars = kRingOff + kRing * kTileBytes;
   static constexpr int kStats = kBars + BAR_COUNT * 8;   // float [3][128]: partial row sums of streams A, B; row max
   static constexpr int kXch = kStats + 3 * 128 * 4;      // float [2 streams][128]: tile maxima, exchanged on a raise
-  static constexpr int kTmemSlot = kXch + 2 * 128 * 4;
+  // 8-bit inputs (the only case with dedicated staging): a second [2][128] block carries the "dominant maximum" flags
+  static constexpr int kTmemSlot = kXch + (STAGE > 0 ? 4 : 2) * 128 * 4;
   // Epilogue staging: 256 rows x (head_dim) bytes of 16-bit output halves.  With 16-bit inputs it is
   // exactly one Q buffer, and the finished item's own Q buffer (idle by then) is used; with 8-bit
   // inputs the Q buffer is half that size and a dedicated area is carved out instead.
@@ -326,12 +327,23 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         // Lazy raise of the shared running max.  One barrier-with-OR per tile between the two warps of
         // this row block tells both whether any of their 64 threads wants a raise (always at the first
         // tile of an item, rarely afterwards); only then are the tile maxima exchanged.
-        const bool want = (m_loc - m_run) > kRescale;
+        bool want = (m_loc - m_run) > kRescale;
+        bool dom = false;
+        if constexpr (kFp8) {
+          // e4m3 P has three mantissa bits: up to 3 % error per element, which only shows in the output of a row
+          // whose mass sits on one or two keys.  A new row maximum that would hold more than an eighth of the mass
+          // accumulated so far therefore becomes the reference point at once (not lazily): its P is then 2^kBias,
+          // exactly representable, and the dominant term of the row carries no rounding error at all.
+          dom = (m_loc > m_run) && (ex2_approx(m_loc - m_run + kBias) > 0.125f * l_run);
+          want = want || dom;
+        }
         if (named_bar_red_or(pair_bar, 64, want)) {
           xch[x * 128 + r_in] = m_loc;
+          if constexpr (kFp8) xch[256 + x * 128 + r_in] = dom ? 1.f : 0.f;
           named_bar_sync(pair_bar, 64);
           const float m_new = fmaxf(m_loc, xch[(x ^ 1) * 128 + r_in]);
-          const bool raise = (m_new - m_run) > kRescale;      // the same decision in both threads of the row
+          bool raise = (m_new - m_run) > kRescale;            // the same decision in both threads of the row
+          if constexpr (kFp8) raise = raise || ((dom || xch[256 + (x ^ 1) * 128 + r_in] != 0.f) && m_new > m_run);
           // everything accumulated relative to the old max is multiplied by alpha = 2^(old - new):
           // the partial row sum and, from the second tile on, this thread's half of the output row
           // (stable once the previous P V is done)
