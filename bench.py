@@ -281,6 +281,88 @@ def _single_gpu_same_workload(shape, dev, attn_fn, steps: int = 3, compare_rows=
     return res, check
 
 
+def _layer_bench(args, shape, world: int, rank: int, dev, steps: int):
+    """The Ulysses layer of the multi-GPU configuration (hidden 5120, 40 heads x 128, QKV and output projections,
+    RMSNorm on q/k, 3-D RoPE, exchange, token-sparse attention with reused metadata and cached residual, exchange
+    back): time per call on N ranks (device time, max over ranks), the same layer on rank 0's GPU alone in the same
+    run, and a comparison of the two results.  Returns the ``layer`` record (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+    from mcsparse_b200 import synth
+    from mcsparse_b200.h3.ulysses_layer import UlyssesDiTAttentionLayer, layer_weights
+    H, L, D, hidden = shape.heads, shape.seq_len, shape.head_dim, shape.heads * shape.head_dim
+    Ls, Hl = L // world, H // world
+    chunks = 5 if Hl % 5 == 0 else 1
+    w = layer_weights(hidden, H, D, seed=0, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    x_full = torch.randn(L, hidden, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)     # same on every rank
+    x = x_full[rank * Ls:(rank + 1) * Ls].contiguous()
+    if rank != 0:
+        del x_full
+    layer = UlyssesDiTAttentionLayer(dist.group.WORLD if world > 1 else None, hidden, H, D, shape.grid, w, dev,
+                                     heads_per_chunk=Hl // chunks)
+    # metadata of the local heads from the layer's own q and k (anchor-step kernels), once, outside the timed region
+    for e in layer.project_and_scatter(x):
+        torch.cuda.current_stream().wait_event(e)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    gi = torch.cat([synth.topmass_indices(layer.local_qkv(c)[0], layer.local_qkv(c)[1], shape) for c in range(layer.chunks)], dim=1)
+    residual = synth.residual_like(shape, heads=Hl, head_offset=rank * Hl, device=dev)
+    layer.set_metadata(gi, residual)
+    for _ in range(3):
+        out = layer.forward(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = layer.forward(x)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    fl = layer.flops(shape.topk)
+    rec = {"workload": f"ulysses_layer_hidden{hidden}_H{H}_D{D}_L{L}_topk{shape.topk}", "n_gpus": world, "ms": ms,
+           "tflops": fl["total"] / (ms * 1e-3) / 1e12, "gemm_flops": fl["gemm"], "attention_flops": fl["attention"],
+           "head_chunks": layer.chunks, "steps": steps,
+           "what": "QKV projection by head chunk (library GEMM) -> RMSNorm + RoPE-3D + peer-store exchange in one kernel per "
+                   "chunk under the next chunk's GEMM -> sparse attention, rows stored into the owners' shards -> output projection"}
+    if world == 1:
+        return rec
+    # all ranks' indices to rank 0, which then runs the whole layer alone
+    gis = [torch.empty_like(gi) for _ in range(world)] if rank == 0 else None
+    dist.gather(gi, gis, dst=0)
+    out_multi = out.clone()
+    del layer
+    torch.cuda.empty_cache()
+    single = None
+    if rank == 0:
+        lay1 = UlyssesDiTAttentionLayer(None, hidden, H, D, shape.grid, w, dev, heads_per_chunk=H // 5 if H % 5 == 0 else 1)
+        lay1.set_metadata(torch.cat(gis, dim=1), synth.residual_like(shape, heads=H, device=dev))
+        for _ in range(2):
+            o1 = lay1.forward(x_full)
+        torch.cuda.synchronize()
+        e0.record()
+        n1 = max(2, min(steps, 3))
+        for _ in range(n1):
+            o1 = lay1.forward(x_full)
+        e1.record()
+        torch.cuda.synchronize()
+        single = e0.elapsed_time(e1) / n1
+        d = (o1[:Ls].float() - out_multi.float()).abs()
+        rec.update({"single_gpu_ms": single, "speedup": single / ms, "efficiency": single / ms / world,
+                    "check": {"against": "the same layer on one GPU, rows of rank 0", "max_abs": float(d.max()),
+                              "mean_rel": float(d.mean() / o1[:Ls].float().abs().mean()),
+                              "ok": bool(float(d.mean() / o1[:Ls].float().abs().mean()) < 1e-2)}})
+        del lay1
+    dist.barrier()
+    return rec if rank == 0 else None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -500,6 +582,14 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms = float(t[0]), float(t[1])
+    layer_rec = None
+    if (world > 1 or args.layer) and not args.no_layer and which == "c5" and not args.heads:
+        # free what the attention-core measurement held, then measure the whole layer
+        if world > 1:
+            del ul, q_s, k_s, v_s
+        del hq, hk, hv, hout
+        torch.cuda.empty_cache()
+        layer_rec = _layer_bench(args, shape, world, rank, dev, steps=max(3, min(args.steps, 10)))
     ms_per_step = total_ms / args.steps
     flops = shape.attn_flops()                      # whole job (all heads, all ranks)
     value = flops / (ms_per_step * 1e-3) / 1e12
@@ -536,6 +626,10 @@ def run_ours(args):
         if check is not None:
             line["check"] = check
             if not check["ok"] or e2e_check is False:
+                rc = 3
+        if layer_rec is not None:
+            line["layer"] = layer_rec
+            if "check" in layer_rec and not layer_rec["check"]["ok"]:
                 rc = 3
         if single is not None:
             line["single_gpu_same_workload"] = single
@@ -804,6 +898,8 @@ def main():
                          "layer, L=98,280 H=40 top-k 4096 in bf16 (default on several GPUs)")
     ap.add_argument("--no-single", action="store_true", help="N > 1: skip rank 0's single-GPU run of the same workload")
     ap.add_argument("--heads", type=int, default=0, help="profiling aid: run a head subset of the workload")
+    ap.add_argument("--layer", action="store_true", help="one GPU with --shape c5: also time the whole Ulysses layer")
+    ap.add_argument("--no-layer", action="store_true", help="N > 1: skip the measurement of the whole layer")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
     ap.add_argument("--e2e-chunk", type=int, default=2, help="heads per chunk of the pipelined end-to-end step (one GPU)")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],

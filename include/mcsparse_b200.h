@@ -164,6 +164,43 @@ int mcs_ulysses_scatter_dma(const void* src, void* const* dst_peers, int32_t n_p
                             int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream);
 
 /*
+ * Epilogue of the QKV projection of a context-parallel attention layer, fused with the sequence-to-head
+ * exchange: for `rows` local tokens and `n_seg` head slices of D elements per token (slice s of token i at
+ * src + i * src_row_stride + s * D, 16-bit elements), query (kind 0) and key (kind 1) slices are RMS-normalised
+ * over their D elements with weights gamma_q / gamma_k (fp32, x * rsqrt(mean(x^2) + eps) * g) and rotated by the
+ * 3-D rotary embedding of the token; value slices (kind 2) are copied.  Slice s of token i is stored at
+ * dst[s] + (row0 + i) * dst_row_stride[s] elements: an address in this GPU's memory or a peer's (see
+ * mcs_gather_attn_fwd_sharded), so every slice lands directly in the (L, heads, D) buffer of the rank that owns
+ * its head.  Token i sits at flattened position token0 + i of a frame-major (grid_f, grid_h, grid_w) grid;
+ * rotation pair p of a slice (elements 2p, 2p+1) follows the frame index for p < pairs_t, the grid row for the
+ * next pairs_h pairs and the grid column for the rest; rope_cs is a device table of (cos, sin) float pairs of
+ * shape (grid_f + grid_h + grid_w, D / 2): row = axis offset + position on that axis, column = pair.
+ * dst, dst_row_stride and kind are HOST arrays of n_seg (<= 128) entries.  D is 64 or 128.
+ *
+ * Replaces: the stretch between the model's QKV projection and the reference's forward_op, i.e. the model's
+ * q/k RMSNorm and rotary embedding followed by the first all-to-all of diffusers'
+ * _templated_context_parallel_attention (mcsparse/h3/context_parallel.py:165-176, 220-229).
+ */
+typedef struct mcs_qkv_epilogue_args {
+  const void* src;
+  const float* gamma_q;
+  const float* gamma_k;
+  const float* rope_cs;
+  void* const* dst;                /* host array, n_seg device pointers */
+  const int64_t* dst_row_stride;   /* host array, elements */
+  const int32_t* kind;             /* host array: 0 query, 1 key, 2 value */
+  int64_t src_row_stride;          /* elements */
+  int64_t rows, row0, token0;
+  int32_t n_seg, D;
+  int32_t grid_f, grid_h, grid_w;
+  int32_t pairs_t, pairs_h;
+  int32_t dtype;                   /* MCS_DTYPE_BF16 or MCS_DTYPE_FP16 */
+  float eps;
+} mcs_qkv_epilogue_args;
+
+int mcs_qkv_norm_rope_scatter(const mcs_qkv_epilogue_args* args, void* stream);
+
+/*
  * Anchor-step group mass: mass[b,h,m,j] = sum_{i in group m} exp(scale * q_i . k_j - lse_i), fp32.
  *
  * Replaces: mcsparse/kernels/flash_mcsa/ops/triton/block_probs.py:27-117

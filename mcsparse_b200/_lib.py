@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "mcs_gather_attn_residual_fwd",
     "mcs_ulysses_scatter",
     "mcs_ulysses_scatter_dma",
+    "mcs_qkv_norm_rope_scatter",
     "mcs_group_mass",
     "mcs_topk_select",
     "mcs_pddp_workspace_bytes",
@@ -60,6 +61,18 @@ class GatherAttnArgs(C.Structure):
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
         ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
         ("softmax_scale", C.c_float), ("flags", C.c_int32),
+    ]
+
+
+class QkvEpilogueArgs(C.Structure):
+    """Mirror of ``mcs_qkv_epilogue_args``."""
+
+    _fields_ = [
+        ("src", C.c_void_p), ("gamma_q", C.c_void_p), ("gamma_k", C.c_void_p), ("rope_cs", C.c_void_p),
+        ("dst", C.POINTER(C.c_void_p)), ("dst_row_stride", C.POINTER(C.c_int64)), ("kind", C.POINTER(C.c_int32)),
+        ("src_row_stride", C.c_int64), ("rows", C.c_int64), ("row0", C.c_int64), ("token0", C.c_int64),
+        ("n_seg", C.c_int32), ("D", C.c_int32), ("grid_f", C.c_int32), ("grid_h", C.c_int32), ("grid_w", C.c_int32),
+        ("pairs_t", C.c_int32), ("pairs_h", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
     ]
 
 
@@ -120,6 +133,8 @@ def lib() -> C.CDLL:
                                       C.c_int64, C.c_int64, C.c_void_p]
     L.mcs_ulysses_scatter_dma.restype = C.c_int
     L.mcs_ulysses_scatter_dma.argtypes = L.mcs_ulysses_scatter.argtypes
+    L.mcs_qkv_norm_rope_scatter.restype = C.c_int
+    L.mcs_qkv_norm_rope_scatter.argtypes = [C.POINTER(QkvEpilogueArgs), C.c_void_p]
     L.mcs_set_clock_buffer.restype = None
     L.mcs_set_clock_buffer.argtypes = [C.c_void_p]
     L.mcs_sm_clock_probe.restype = C.c_int

@@ -166,6 +166,33 @@ int mcs_ulysses_scatter_dma(const void* src, void* const* dst_peers, int32_t n_p
   return ulysses_scatter_checked(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, stream, true);
 }
 
+int mcs_qkv_norm_rope_scatter(const mcs_qkv_epilogue_args* a, void* stream) {
+  if (a == nullptr || a->src == nullptr || a->dst == nullptr || a->dst_row_stride == nullptr || a->kind == nullptr ||
+      a->rope_cs == nullptr || a->gamma_q == nullptr || a->gamma_k == nullptr)
+    return MCS_ERR_NULL_POINTER;
+  if (a->rows < 0 || a->n_seg < 1 || a->n_seg > mcs::kQkvMaxSegments || a->row0 < 0 || a->token0 < 0) return MCS_ERR_BAD_SHAPE;
+  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
+  if (a->grid_f < 1 || a->grid_h < 1 || a->grid_w < 1 || a->pairs_t < 0 || a->pairs_h < 0 || a->pairs_t + a->pairs_h > a->D / 2)
+    return MCS_ERR_BAD_SHAPE;
+  if (a->token0 + a->rows > (int64_t)a->grid_f * a->grid_h * a->grid_w) return MCS_ERR_BAD_SHAPE;
+  if (a->src_row_stride < (int64_t)a->n_seg * a->D || a->src_row_stride % 8 || !aligned16(a->src)) return MCS_ERR_BAD_ALIGNMENT;
+  if (!(a->eps >= 0.f) || !std::isfinite(a->eps)) return MCS_ERR_BAD_SCALE;
+  long long strides[mcs::kQkvMaxSegments];
+  for (int i = 0; i < a->n_seg; ++i) {
+    if (a->dst[i] == nullptr) return MCS_ERR_NULL_POINTER;
+    if (!aligned16(a->dst[i]) || a->dst_row_stride[i] % 8 || a->dst_row_stride[i] < a->D) return MCS_ERR_BAD_ALIGNMENT;
+    if (a->kind[i] < 0 || a->kind[i] > 2) return MCS_ERR_BAD_SHAPE;
+    strides[i] = a->dst_row_stride[i];
+  }
+  mcs::QkvEpilogueParams p{};
+  p.src = a->src; p.src_row_stride = a->src_row_stride; p.rows = a->rows; p.row0 = a->row0; p.token0 = a->token0;
+  p.gamma_q = a->gamma_q; p.gamma_k = a->gamma_k; p.rope_cs = reinterpret_cast<const float2*>(a->rope_cs);
+  p.n_seg = a->n_seg; p.D = a->D; p.grid_f = a->grid_f; p.grid_h = a->grid_h; p.grid_w = a->grid_w;
+  p.pairs_t = a->pairs_t; p.pairs_h = a->pairs_h; p.eps = a->eps;
+  return mcs::launch_qkv_epilogue(p, a->dst, strides, a->kind, a->dtype == MCS_DTYPE_FP16, static_cast<cudaStream_t>(stream));
+}
+
 int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {
   if (a == nullptr || a->q == nullptr || a->k == nullptr || a->lse == nullptr || a->mass == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;

@@ -112,6 +112,25 @@ int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
 
+// QKV-projection epilogue: RMSNorm + 3-D rotary embedding + store into the (peer) buffers the attention reads (qkv_epilogue.cu)
+constexpr int kQkvMaxSegments = 128;
+struct QkvEpilogueParams {
+  const void* src;            // (rows, n_seg, D) 16-bit, row stride src_row_stride elements
+  long long src_row_stride;
+  long long rows;
+  long long row0;             // destination row of local row 0 (rank * rows in a sequence-sharded layer)
+  long long token0;           // grid position (flattened, frame-major) of local row 0
+  const float* gamma_q;       // (D) RMSNorm weights of query slices
+  const float* gamma_k;       // (D) RMSNorm weights of key slices
+  const float2* rope_cs;      // (grid_f + grid_h + grid_w, D / 2) (cos, sin) per axis position and rotation pair
+  int n_seg, D;
+  int grid_f, grid_h, grid_w; // tokens are numbered frame-major over this grid
+  int pairs_t, pairs_h;       // rotation pairs [0, pairs_t) follow the frame, the next pairs_h the row, the rest the column
+  float eps;
+};
+int launch_qkv_epilogue(const QkvEpilogueParams& p, void* const* dst, const long long* dst_row_stride, const int* kind,
+                        bool fp16, cudaStream_t stream);
+
 // Sequence-to-head reshard by peer stores (see reshard.cu)
 int launch_ulysses_scatter_dma(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
                                long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);

@@ -90,6 +90,27 @@ def _worker(rank, world, port, q):
         st = tsd.get_mcsa_token_stats()
         ok = ok and cp.get_cp_stats() == {"cp_calls": 3, "local_calls": 0} and st["kernel_calls"] == 3 and st["calibrate_calls"] == 1
         ok = ok and single_stats["kernel_calls"] == 3
+        # ---- (3) the whole layer on real peers == the same layer on one GPU (rows of this rank), to GEMM rounding
+        from mcsparse_b200.h3.ulysses_layer import UlyssesDiTAttentionLayer, layer_weights
+        grid, hidden = (8, 16, 64), 1024
+        H2 = 2 * world * 2
+        w = layer_weights(hidden, H2, D, seed=1, device=dev)
+        x = torch.randn(L, hidden, generator=g, device=dev).to(torch.bfloat16)
+        gi2 = torch.cat([synth.random_sorted_indices(1, 1, L // 128, topk, L, seed=50 + h, device=dev) for h in range(H2)], dim=1)
+        res2 = (0.1 * torch.randn(1, H2, L, D, generator=g, device=dev)).to(torch.bfloat16)
+        one = UlyssesDiTAttentionLayer(None, hidden, H2, D, grid, w, dev, heads_per_chunk=2)
+        one.set_metadata(gi2, res2)
+        want_l = one.forward(x)
+        Hl2 = H2 // world
+        lay = UlyssesDiTAttentionLayer(dist.group.WORLD, hidden, H2, D, grid, w, dev, heads_per_chunk=2)
+        lay.set_metadata(gi2[:, rank * Hl2:(rank + 1) * Hl2].contiguous(), res2[:, rank * Hl2:(rank + 1) * Hl2].contiguous())
+        for _ in range(2):
+            got_l = lay.forward(x[rank * Ls:(rank + 1) * Ls].contiguous())
+        torch.cuda.synchronize()
+        dl = (got_l.float() - want_l[rank * Ls:(rank + 1) * Ls].float()).abs()
+        rel = float(dl.mean() / want_l.float().abs().mean())
+        ok = ok and rel < 1e-2
+        notes.append(f"layer: mean-rel diff {rel:.2e}, max {float(dl.max()):.2e}")
         _lib.check_status(dev, "multi-gpu test")
         q.put((rank, bool(ok), notes))
     except Exception as e:                                                    # report instead of hanging the peers
