@@ -19,7 +19,8 @@
 // columns are (1, 1, 1, 0, ...) and whose Q columns are (-hi, -mid, -lo, 0, ...), a three-term
 // bf16 split of lse_i / scale, exact to fp32 precision.  The tensor core then delivers
 // q_i . k_j - lse_i / scale and each element costs one multiply, one ex2 and one add.
-// The kernel is bound by the ex2 throughput of the SFU (16 per clock per SM).
+// The kernel is bound by the ex2 throughput of the SFU (16 per clock per SM); a quarter of the exponentials
+// are therefore evaluated by a polynomial on the FMA pipe.
 //
 // Roles: warps 0-7 exponentiate and sum (two threads per key token: warps w and w+4 share a TMEM
 // lane group and take 64 query columns each, so that every SM sub-partition has two warps feeding
@@ -69,7 +70,7 @@ __device__ __forceinline__ uint32_t swz(int row, int c) {   // 16-byte chunk c o
   return static_cast<uint32_t>((c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
 
-template <int D, bool kFp16>
+template <int D, bool kFp16, int kPoly>
 __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMassParams p, const __grid_constant__ KeyTileMap kmap) {
   // key tiles are 128 consecutive rows: with a valid tensor map one elected thread loads them by TMA
   const bool use_tma = kmap.valid != 0;
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
     const int j_in = lg * 32 + lane;                   // key token inside the tile == TMEM lane
     const uint32_t lane_addr = (static_cast<uint32_t>(lg) * 32u) << 16;
     const float c = p.scale_log2;
+    const float xmin = -125.f / c;
     const float norm = p.normalize ? 1.f / static_cast<float>(rows_valid) : 1.f;
     float* out = p.mass + ((size_t)bh * p.M + m) * p.Lk;
     float* part = reinterpret_cast<float*>(smem + L::kPart);
@@ -137,11 +139,18 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
         tmem_ld32(tmem + buf * 128 + x * 64 + q * 32 + lane_addr, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          a0 += ex2_approx(__uint_as_float(r[i]) * c);
-          a1 += ex2_approx(__uint_as_float(r[i + 1]) * c);
-          a2 += ex2_approx(__uint_as_float(r[i + 2]) * c);
-          a3 += ex2_approx(__uint_as_float(r[i + 3]) * c);
+        for (int i = 0; i < 32; i += 8) {
+          // kPoly of every eight exponentials are computed on the FMA pipe instead of the special-function unit,
+          // which bounds this kernel (see ex2_poly3_scaled); their positions are spread over the four partial sums.
+          // Two of eight measured best (7.84 ms against 8.29 ms with none and 8.10 / 8.36 ms with three / four at
+          // H=24, L=32,760: beyond a quarter the extra instructions cost more issue slots than the unit gains).
+          auto e = [&](int k) {
+            const float v = __uint_as_float(r[i + k]);
+            const bool poly = (kPoly >= 1 && k == 3) || (kPoly >= 2 && k == 6) || (kPoly >= 3 && k == 1) || (kPoly >= 4 && k == 4);
+            return poly ? ex2_poly3_scaled(v, c, xmin) : ex2_approx(v * c);
+          };
+          a0 += e(0); a1 += e(1); a2 += e(2); a3 += e(3);
+          a0 += e(4); a1 += e(5); a2 += e(6); a3 += e(7);
         }
       }
       tc_fence_before();
@@ -327,10 +336,10 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
   }
 }
 
-template <int D, bool kFp16>
+template <int D, bool kFp16, int kPoly = 2>
 int launch(const GroupMassParams& p, cudaStream_t stream) {
   using L = Smem<D>;
-  auto kern = group_mass_kernel<D, kFp16>;
+  auto kern = group_mass_kernel<D, kFp16, kPoly>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return -8;
   const long long grid = (long long)p.B * p.H * p.M;
   KeyTileMap kmap{};

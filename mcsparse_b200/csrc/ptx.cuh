@@ -346,6 +346,23 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 // Three-input maximum (one instruction on sm_100).
+// 2^(x * c) without the special-function unit, for x * c >= -125 (xmin = -125 / c clamps the input; the result of
+// anything below is 2^-125, i.e. nothing): x * c = n + f with n = round(x * c), |f| <= 1/2; 2^f by a cubic polynomial
+// (largest relative error 7.5e-5); 2^n by adding n to the exponent field.  Five instructions on the FMA pipe, one
+// clamp and two integer operations, against one instruction that holds the special-function unit for eight cycles
+// per warp: where a kernel is bound by ex2 (16 results per clock and SM), a share of the elements goes this way.
+// The reference carries a helper of the same purpose (ex2_emulation,
+// mcsparse/kernels/flash_mcsa/ops/flash_sparse_attn/cute/utils.py:696-843).
+__device__ __forceinline__ float ex2_poly3_scaled(float x, float c, float xmin) {
+  x = fmaxf(x, xmin);
+  const float t = fmaf(x, c, 12582912.f);          // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float r = t - 12582912.f;
+  const float f = fmaf(x, c, -r);
+  float p = fmaf(0.05517100170254707f, f, 0.24260950088500977f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999281764030457f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
