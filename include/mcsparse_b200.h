@@ -245,6 +245,30 @@ int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int
                     int64_t rows, int32_t L, int32_t k_total, void* stream);
 
 /*
+ * The same selection with a budget of its own for every row: row r gets the sinks plus its (k_rows[r] - n_sink)
+ * best other tokens, ascending, in out[r * k_max ...]; the entries from k_rows[r] up to k_max are set to 0 (the
+ * attention kernel never reads them: the caller passes ceil-free tile counts k_rows[r] / 128 as gather_kv_lengths).
+ * k_rows is a device array of `rows` int32, each clamped to [n_sink, k_max].
+ *
+ * Replaces: the variable-length branches of mcsparse/kernels/flash_mcsa/token_sparse.py:755-945 (per-head budgets
+ * :825-835, top-p :842-852, top-k-or-top-p :854-876, padding :924-934), where the reference sorts every row in full
+ * and slices prefixes of different lengths.
+ */
+int mcs_topk_select_var(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink, int64_t rows,
+                        int32_t L, int32_t k_max, const int32_t* k_rows, void* stream);
+
+/*
+ * Top-p budgets: counts[r] = number of leading tokens of row r, in descending order of score, whose scores summed
+ * BEFORE each of them stay below topp (at least 1, everything if the row's total stays below topp); sink tokens are
+ * left out of the ranking and of the count.  scores: (rows, L) fp32 normalised masses; 0 < topp <= 1.
+ *
+ * Replaces: the sort + cumulative sum + mask count of mcsparse/kernels/flash_mcsa/token_sparse.py:842-852 and
+ * :862-866 (topp / topk_topp modes); the tile alignment and the lower bound of topk_topp stay on the host.
+ */
+int mcs_topp_count(const float* scores, const int32_t* sinks, int32_t n_sink, int64_t rows, int32_t L, float topp,
+                   int32_t* counts, void* stream);
+
+/*
  * Fast PDDP query grouping: per (batch*head) permutation that puts similar rows into aligned
  * blocks of C rows by recursive principal-direction bisection.
  *

@@ -35,6 +35,8 @@ EXPORTED_SYMBOLS = (
     "mcs_qkv_norm_rope_scatter",
     "mcs_group_mass",
     "mcs_topk_select",
+    "mcs_topk_select_var",
+    "mcs_topp_count",
     "mcs_pddp_workspace_bytes",
     "mcs_pddp_start_vector_rows",
     "mcs_pddp_levels",
@@ -144,6 +146,11 @@ def lib() -> C.CDLL:
     L.mcs_topk_select.restype = C.c_int
     L.mcs_topk_select.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                   C.c_void_p]
+    L.mcs_topk_select_var.restype = C.c_int
+    L.mcs_topk_select_var.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                      C.c_void_p, C.c_void_p]
+    L.mcs_topp_count.restype = C.c_int
+    L.mcs_topp_count.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_void_p]
     L.mcs_pddp_workspace_bytes.restype = C.c_int64
     L.mcs_pddp_workspace_bytes.argtypes = [C.c_int32] * 3
     L.mcs_pddp_start_vector_rows.restype = C.c_int64

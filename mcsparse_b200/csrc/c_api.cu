@@ -221,8 +221,25 @@ int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int
   if (scores == nullptr || out == nullptr || (n_sink > 0 && sinks == nullptr)) return MCS_ERR_NULL_POINTER;
   if (rows < 0 || L < 1 || n_sink < 0 || n_sink > 64 || k_total < n_sink || k_total > L) return MCS_ERR_BAD_SHAPE;
   if (rows == 0) return 0;
-  mcs::TopkParams p{scores, out, sinks, (long long)rows, L, k_total, n_sink};
+  mcs::TopkParams p{scores, out, sinks, (long long)rows, L, k_total, n_sink, nullptr};
   return mcs::launch_topk_select(p, static_cast<cudaStream_t>(stream));
+}
+
+int mcs_topk_select_var(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink, int64_t rows, int32_t L,
+                        int32_t k_max, const int32_t* k_rows, void* stream) {
+  if (scores == nullptr || out == nullptr || k_rows == nullptr || (n_sink > 0 && sinks == nullptr)) return MCS_ERR_NULL_POINTER;
+  if (rows < 0 || L < 1 || n_sink < 0 || n_sink > 64 || k_max < n_sink || k_max > L) return MCS_ERR_BAD_SHAPE;
+  if (rows == 0) return 0;
+  mcs::TopkParams p{scores, out, sinks, (long long)rows, L, k_max, n_sink, k_rows};
+  return mcs::launch_topk_select(p, static_cast<cudaStream_t>(stream));
+}
+
+int mcs_topp_count(const float* scores, const int32_t* sinks, int32_t n_sink, int64_t rows, int32_t L, float topp, int32_t* counts,
+                   void* stream) {
+  if (scores == nullptr || counts == nullptr || (n_sink > 0 && sinks == nullptr)) return MCS_ERR_NULL_POINTER;
+  if (rows < 0 || L < 1 || n_sink < 0 || n_sink > 64 || n_sink >= L) return MCS_ERR_BAD_SHAPE;
+  if (!(topp > 0.f) || !(topp <= 1.f)) return MCS_ERR_BAD_SCALE;
+  return mcs::launch_topp_count(scores, sinks, n_sink, (long long)rows, L, topp, counts, static_cast<cudaStream_t>(stream));
 }
 
 int64_t mcs_pddp_workspace_bytes(int32_t BH, int32_t N, int32_t C) { return (int64_t)mcs::pddp_workspace_bytes(BH, N, C); }

@@ -105,7 +105,10 @@ struct TopkParams {
   const int32_t* sinks;  // n_sink distinct indices in [0, L)
   long long rows;
   int L, k_total, n_sink;
+  const int32_t* k_rows;  // optional per-row budgets (sinks included), clamped to [n_sink, k_total]; entries beyond are zeroed
 };
+int launch_topp_count(const float* scores, const int32_t* sinks, int n_sink, long long rows, int L, float topp, int32_t* counts,
+                      cudaStream_t stream);
 
 int launch_topk_select(const TopkParams& p, cudaStream_t stream);
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);

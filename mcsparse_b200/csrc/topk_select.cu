@@ -55,7 +55,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_select_kernel(const TopkPara
   uint32_t* skeys = reinterpret_cast<uint32_t*>(smem_raw + sizeof(Shared));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int L = p.L, n_sink = p.n_sink;
-  const int k = p.k_total - n_sink;                       // non-sink tokens to pick (>= 0, <= L - n_sink)
 
   if (tid < n_sink) sh.sinks[tid] = p.sinks[tid];
   __syncthreads();
@@ -64,6 +63,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_select_kernel(const TopkPara
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const float* sc = p.scores + row * (long long)L;
     int32_t* out = p.out + row * (long long)p.k_total;
+    // this row's budget (sinks included): the common k_total, or its own entry of k_rows
+    const int k_row = p.k_rows != nullptr ? min(max(p.k_rows[row], n_sink), p.k_total) : p.k_total;
+    const int k = k_row - n_sink;                         // non-sink tokens to pick (>= 0, <= L - n_sink)
 
     auto is_sink = [&](int j) {
       bool s = false;
@@ -169,11 +171,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_select_kernel(const TopkPara
       const uint32_t sel_b = __ballot_sync(0xffffffffu, sel);
       if (sel) {
         const int pos = out_before + __popc(sel_b & ((1u << lane) - 1u));
-        if (pos < p.k_total) out[pos] = j;
+        if (pos < k_row) out[pos] = j;
       }
       eq_before += __popc(eq_b);
       out_before += __popc(sel_b);
     }
+    for (int i = k_row + tid; i < p.k_total; i += kThreads) out[i] = 0;      // beyond the row's own budget: padding
     __syncthreads();                                       // shared state is reused by the next row
   }
 }
@@ -306,7 +309,6 @@ __global__ void __launch_bounds__(kRT, 1) topk_select_reg_kernel(const TopkParam
   float* stage = reinterpret_cast<float*>(ckeys + kCandCap);             // one row of scores, swizzled
   const int tid = threadIdx.x;
   const int L = p.L, n_sink = p.n_sink;
-  const int k = p.k_total - n_sink;
   const int j0 = tid * kKpt;                                             // this thread owns scores [j0, j0 + 32)
 
   // The next row streams into shared memory (cp.async) while the current one is processed out of
@@ -332,6 +334,8 @@ __global__ void __launch_bounds__(kRT, 1) topk_select_reg_kernel(const TopkParam
 #pragma unroll 1
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
     int32_t* out = p.out + row * (long long)p.k_total;
+    const int k_row = p.k_rows != nullptr ? min(max(p.k_rows[row], n_sink), p.k_total) : p.k_total;
+    const int k = k_row - n_sink;
     cp_async_wait_all();
     __syncthreads();
     // ---- keys into registers: slot q holds score j0 + q; padding beyond L gets the lowest key
@@ -459,9 +463,10 @@ __global__ void __launch_bounds__(kRT, 1) topk_select_reg_kernel(const TopkParam
       const bool is_eq = (eq_mask >> q) & 1ull;
       if (!is_eq || e_b < (uint32_t)need) {
         const uint32_t pos = s_b + min(e_b, (uint32_t)need);
-        if (pos < (uint32_t)p.k_total) out[pos] = j0 + q;
+        if (pos < (uint32_t)k_row) out[pos] = j0 + q;
       }
     }
+    for (int i = k_row + tid; i < p.k_total; i += kRT) out[i] = 0;           // beyond the row's own budget: padding
   }
   cp_async_wait_all();
 }

@@ -123,37 +123,121 @@ def select_topk_with_sinks(scores: torch.Tensor, k_total: int, sink_ranges=None,
     return out
 
 
+def topp_count(scores: torch.Tensor, topp: float, sink_ranges=None) -> torch.Tensor:
+    """Per row of normalised fp32 masses (..., L): how many tokens, taken in descending order of mass, are needed
+    before the mass in front of the next one reaches ``topp`` (at least 1; sinks are not ranked or counted).
+    Returns int32 (...)."""
+    if scores.dtype != torch.float32 or not scores.is_cuda:
+        raise TypeError("scores must be a float32 CUDA tensor")
+    L = scores.shape[-1]
+    sinks = _sink_indices(sink_ranges, L)
+    if len(sinks) > 64:
+        raise ValueError("at most 64 sink tokens are supported")
+    scores = scores.contiguous()
+    rows = scores.numel() // L
+    out = torch.empty(scores.shape[:-1], dtype=torch.int32, device=scores.device)
+    sink_t = torch.tensor(sinks, dtype=torch.int32, device=scores.device) if sinks else None
+    stream = torch.cuda.current_stream(scores.device).cuda_stream
+    rc = _lib.lib().mcs_topp_count(scores.data_ptr(), None if sink_t is None else sink_t.data_ptr(), len(sinks), rows, L,
+                                   float(topp), out.data_ptr(), stream)
+    _lib.raise_on_error(rc, "topp_count")
+    if _lib.check_enabled():
+        _lib.check_status(scores.device, "topp_count")
+    return out
+
+
+def select_topk_var(scores: torch.Tensor, k_rows: torch.Tensor, k_max: int, sink_ranges=None) -> torch.Tensor:
+    """Selection with a budget per row: row r gets the sinks plus its ``k_rows[r] - n_sink`` best other tokens,
+    ascending, padded with zeros to ``k_max``.  scores (..., L) fp32, k_rows (...) int32.  Returns (..., k_max) int32."""
+    if scores.dtype != torch.float32 or not scores.is_cuda:
+        raise TypeError("scores must be a float32 CUDA tensor")
+    L = scores.shape[-1]
+    sinks = _sink_indices(sink_ranges, L)
+    if len(sinks) > 64:
+        raise ValueError("at most 64 sink tokens are supported")
+    if tuple(k_rows.shape) != tuple(scores.shape[:-1]):
+        raise ValueError("one budget per score row")
+    if not (len(sinks) <= k_max <= L):
+        raise ValueError(f"k_max must be in [n_sink={len(sinks)}, L={L}], got {k_max}")
+    scores = scores.contiguous()
+    k_rows = k_rows.to(torch.int32).contiguous()
+    rows = scores.numel() // L
+    out = torch.empty(tuple(scores.shape[:-1]) + (k_max,), dtype=torch.int32, device=scores.device)
+    sink_t = torch.tensor(sinks, dtype=torch.int32, device=scores.device) if sinks else None
+    stream = torch.cuda.current_stream(scores.device).cuda_stream
+    rc = _lib.lib().mcs_topk_select_var(scores.data_ptr(), out.data_ptr(), None if sink_t is None else sink_t.data_ptr(),
+                                        len(sinks), rows, L, int(k_max), k_rows.data_ptr(), stream)
+    _lib.raise_on_error(rc, "select_topk_var")
+    if _lib.check_enabled():
+        _lib.check_status(scores.device, "select_topk_var")
+    return out
+
+
+def selection_counts(L_K: int, n_sink: int, tile_n: int, base_counts: torch.Tensor) -> torch.Tensor:
+    """Budget arithmetic of the variable-length modes (token_sparse.py:811-823, :902-923): the per-row number of
+    ranked tokens is rounded up to whole tiles (never beyond L_K), the sinks are added, the total is rounded up to whole
+    tiles again as long as ranked tokens are left to fill it, else down, and it is at least one tile."""
+    c = base_counts.long().clamp(min=1)
+    c = (((c + tile_n - 1) // tile_n) * tile_n).clamp(max=L_K)
+    avail = int(c.max().item()) + n_sink                      # length of [sinks, ranked prefix] in the reference
+    if n_sink:
+        c = (((c + n_sink + tile_n - 1) // tile_n) * tile_n).clamp(max=avail)
+    cap = max(tile_n, min(((L_K + tile_n - 1) // tile_n) * tile_n, (avail // tile_n) * tile_n))
+    c = c.clamp(min=tile_n, max=cap)
+    return ((c // tile_n) * tile_n).clamp(max=L_K)
+
+
 def _select_topk_tokens(token_probs, topk_ratio, tile_n=128, ds_k=1, orig_L_K=None,
                         selection_mode='topk', topp=None, sink_ranges=None):
-    """Reference-shaped selection (token_sparse.py:755-945), ``topk`` mode, scalar ratio, ds_k == 1.
+    """Reference-shaped selection (token_sparse.py:755-945), ds_k == 1.
 
-    Budget arithmetic as in the reference: ``k_sel = min(L_K, align_up(max(1, int(ratio * L_K)), tile_n))``;
-    with sinks the list ``[sinks, top-k_sel]`` is cut to a whole number of tiles and tile counts are
-    returned, without sinks the counts are None.  Where the reference drops an arbitrary subset of an
-    unsorted top-k, this drops the lowest-ranked entries, and indices come back ascending.
+    ``topk`` with a scalar ratio: ``k_sel = min(L_K, align_up(max(1, int(ratio * L_K)), tile_n))``; with sinks the list
+    ``[sinks, top-k_sel]`` is cut to a whole number of tiles and tile counts are returned, without sinks the counts are
+    None.  ``topk`` with a (B, H) ratio tensor (adaptive heads), ``topp`` (shortest prefix of the descending order
+    that reaches mass ``topp``) and ``topk_topp`` (the same with the top-k budget as lower bound) give every row its
+    own budget: rounded up to whole tiles with real tokens, tile counts returned, rows padded with zeros beyond them.
+    Where the reference keeps an arbitrary subset of an unsorted top-k or a descending prefix, this keeps the
+    best-ranked tokens (ties to the lowest index) and returns them ascending.
     Returns ``(gather_indices (B,H,M,gather_len) int32, gather_kv_lengths (B,H,M) int32 | None)``.
     """
-    if selection_mode != 'topk':
-        raise NotImplementedError(f"selection_mode={selection_mode!r}: only 'topk' runs on this path")
+    if selection_mode not in ('topk', 'topp', 'topk_topp'):
+        raise ValueError(f"Unknown selection_mode: {selection_mode}")
     if ds_k != 1:
         raise NotImplementedError("key downsampling (ds_k > 1) is not part of this path")
-    if isinstance(topk_ratio, torch.Tensor):
-        raise NotImplementedError("adaptive per-head budgets are not part of this path")
     B, H, M, L_K = token_probs.shape
-    n = max(1, int(topk_ratio * L_K))
-    k_sel = min(((n + tile_n - 1) // tile_n) * tile_n, L_K)
     sinks = _sink_indices(sink_ranges, L_K)
     scores = token_probs.float()
-    if not sinks:
-        gl = k_sel if k_sel % tile_n == 0 else max(tile_n, (k_sel // tile_n) * tile_n)
-        return select_topk_with_sinks(scores, min(gl, L_K)), None
-    total = k_sel + len(sinks)
-    cap = max(tile_n, min(((L_K + tile_n - 1) // tile_n) * tile_n, (total // tile_n) * tile_n))
-    count = min(max(min(((total + tile_n - 1) // tile_n) * tile_n, total), tile_n), cap)
-    count = min(count, L_K)
-    gi = select_topk_with_sinks(scores, count, sink_ranges)
-    lengths = torch.full((B, H, M), count // tile_n, dtype=torch.int32, device=token_probs.device)
-    return gi, lengths
+    adaptive = isinstance(topk_ratio, torch.Tensor)
+    if selection_mode == 'topk' and not adaptive:
+        n = max(1, int(topk_ratio * L_K))
+        k_sel = min(((n + tile_n - 1) // tile_n) * tile_n, L_K)
+        if not sinks:
+            gl = k_sel if k_sel % tile_n == 0 else max(tile_n, (k_sel // tile_n) * tile_n)
+            return select_topk_with_sinks(scores, min(gl, L_K)), None
+        total = k_sel + len(sinks)
+        cap = max(tile_n, min(((L_K + tile_n - 1) // tile_n) * tile_n, (total // tile_n) * tile_n))
+        count = min(max(min(((total + tile_n - 1) // tile_n) * tile_n, total), tile_n), cap)
+        count = min(count, L_K)
+        gi = select_topk_with_sinks(scores, count, sink_ranges)
+        lengths = torch.full((B, H, M), count // tile_n, dtype=torch.int32, device=token_probs.device)
+        return gi, lengths
+    # ---- every row with a budget of its own
+    if selection_mode == 'topk':
+        base = (topk_ratio.to(scores.device).float() * L_K).long().view(B, H, 1).expand(B, H, M)
+    else:
+        if topp is None:
+            raise AssertionError(f"{selection_mode} mode requires topp")
+        base = topp_count(scores, topp, sink_ranges).long()
+        if selection_mode == 'topk_topp':
+            if adaptive:
+                floor_k = (topk_ratio.to(scores.device).float() * L_K).clamp(min=1, max=L_K).long().view(B, H, 1).expand(B, H, M)
+            else:
+                floor_k = torch.full_like(base, min(max(1, int(topk_ratio * L_K)), L_K))
+            base = torch.maximum(base, floor_k)
+    counts = selection_counts(L_K, len(sinks), tile_n, base)
+    k_max = int(counts.max().item())
+    gi = select_topk_var(scores, counts.to(torch.int32), k_max, sink_ranges)
+    return gi, (counts // tile_n).to(torch.int32).contiguous()
 
 
 def _compute_adaptive_topk_token(token_probs, base_topk, layer_t=None):

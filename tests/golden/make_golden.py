@@ -46,6 +46,25 @@ def main():
         sel.append({"L": L, "ratio": ratio, "sinks": sinks, "seed": seed, "gi": gi, "gl": gl})
     torch.save(sel, HERE / "select_reference.pt")
     print("wrote", HERE / "pddp_reference.pt", HERE / "select_reference.pt")
+    # ---- variable-length selection modes on normalised probabilities
+    modes = []
+    for (L, mode, ratio, topp, sinks, seed) in [(1536, "topp", 0.1, 0.6, None, 11), (2000, "topp", 0.1, 0.9, [(0, 4)], 12),
+                                                (1536, "topk_topp", 0.25, 0.5, [(0, 4)], 13), (1024, "topk_topp", 0.05, 0.8, None, 14),
+                                                (1536, "topk", "adaptive", None, [(0, 4)], 15), (2048, "topk_topp", "adaptive", 0.7, None, 16)]:
+        g = torch.Generator().manual_seed(seed)
+        # peaked rows: a softmax over scaled logits so that top-p prefixes have very different lengths
+        tp = torch.softmax(torch.randn(1, 2, 3, L, generator=g) * torch.tensor([1.0, 3.0]).view(1, 2, 1, 1), dim=-1)
+        r = torch.tensor([[0.08, 0.3]]) if ratio == "adaptive" else ratio
+        gi, gl = _select_topk_tokens(tp, r, selection_mode=mode, topp=topp, sink_ranges=sinks)
+        modes.append({"L": L, "mode": mode, "ratio": ratio, "topp": topp, "sinks": sinks, "seed": seed, "gi": gi, "gl": gl})
+    # per-head budgets from retained mass (adaptive heads), with and without layer depth
+    from mcsparse.kernels.flash_mcsa.token_sparse import _compute_adaptive_topk_token
+    g = torch.Generator().manual_seed(21)
+    tp = torch.softmax(torch.randn(2, 4, 3, 1024, generator=g) * torch.tensor([0.5, 1.0, 2.0, 4.0]).view(1, 4, 1, 1), dim=-1)
+    modes.append({"mode": "adaptive_ratio", "seed": 21, "base": 0.1,
+                  "ratio": _compute_adaptive_topk_token(tp, 0.1), "ratio_t": _compute_adaptive_topk_token(tp, 0.1, layer_t=0.25)})
+    torch.save(modes, HERE / "select_modes_reference.pt")
+    print("wrote", HERE / "select_modes_reference.pt")
     mass_golden()
 
 
