@@ -14,8 +14,8 @@ Mirrored host logic: the schedule translation of ``dense_steps`` / ``dense_layer
 (:561-632) and its validation (:635-666), the effective density (:669-689), the eligibility table with its
 two severities (:696-772; a call under context parallelism is ineligible here and belongs to
 ``mcsparse_b200.h3.context_parallel.with_ulysses_sparse``), the query-side prefix splice for
-``sink_tokens > 0`` (:1086-1124) and ``ticks_per_step`` (:274-309).  Index/residual offload knobs are accepted
-and ignored: all metadata stays resident in HBM on this part.
+``sink_tokens > 0`` (:1086-1124) and ``ticks_per_step`` (:274-309).  The index / residual offload knobs work as in
+the reference but default to off: on a 180 GB part the metadata normally stays in HBM.
 
 One addition: a kernel problem (a negative return code of the C ABI, or a non-zero device status word) is
 counted in ``kernel_error_calls`` and ``fallback_calls`` and the call is served by the original dispatch.
@@ -201,9 +201,9 @@ def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 
     ``dense_layers`` / ``calibrate_every`` / ``calibrate_steps`` go through :func:`build_schedule`;
     ``full_steps`` / ``full_layers`` / ``sink_ranges`` may instead be given directly.  ``context`` may inject a
     ready TokenSparseContext-like object (``forward(li, q, k, v, scale)``, ``caches[li].mode``, ``step()``,
-    ``reset()``), which the CPU tests use.  ``offload_indices`` / ``cache_offload`` / ``offload_prefetch_ahead``
-    / ``full_attn_impl`` are accepted for call compatibility and have no effect: metadata stays in HBM and
-    there is one dense implementation.
+    ``reset()``), which the CPU tests use.  ``offload_indices`` / ``cache_offload`` / ``offload_prefetch_ahead`` park
+    indices / residual in pinned host memory between uses (default off); ``full_attn_impl`` is accepted for call
+    compatibility and has no effect: there is one dense implementation.
     """
     sink_tokens = int(sink_tokens)
     if sink_tokens < 0:
@@ -247,7 +247,9 @@ def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 
                                 full_steps=full_steps, full_layers=sorted(full_layers_set), sink_ranges=sink_ranges,
                                 bias_correction=bias_correction, pca_reorder=pca_reorder, pca_pow_iters=pca_pow_iters,
                                 pca_proj_dim=pca_proj_dim, adaptive_layers=adaptive_layers,
-                                use_chunk_selector=use_chunk_selector, chunk_selector_size=chunk_selector_size)
+                                use_chunk_selector=use_chunk_selector, chunk_selector_size=chunk_selector_size,
+                                offload_indices=offload_indices, cache_offload=cache_offload,
+                                offload_prefetch_ahead=offload_prefetch_ahead)
         context = TokenSparseContext(cfg, num_layers)
     if _CTX["ctx"] is not None and hasattr(_CTX["ctx"], "reset"):
         _CTX["ctx"].reset()                                       # release the previous context's caches first

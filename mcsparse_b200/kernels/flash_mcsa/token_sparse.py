@@ -338,6 +338,9 @@ class TokenSparseConfig:
     pca_pow_iters: int = 4
     pca_seed: int = 0
     pca_proj_dim: Optional[int] = None
+    offload_indices: bool = False          # keep the indices in pinned host memory between uses (reference default: True)
+    cache_offload: str = 'none'            # 'residual': the same for the bias-correction residual
+    offload_prefetch_ahead: int = 1        # layers ahead of its use at which an offloaded tensor starts to come back
 
     def __post_init__(self):
         assert 0 < self.topk <= 1.0
@@ -366,6 +369,10 @@ class TokenSparseConfig:
         if self.pca_reorder:
             assert not self.share_lse, "pca_reorder is incompatible with share_lse"
         assert self.chunk_selector_size > 0 and self.chunk_selector_size % self.tile_n == 0
+        assert self.cache_offload in ('none', 'residual'), f"cache_offload must be 'none' or 'residual', got {self.cache_offload!r}"
+        assert self.offload_prefetch_ahead in (0, 1), "offload_prefetch_ahead only supports 0 or 1"
+        if self.cache_offload == 'residual':
+            assert self.bias_correction, "cache_offload='residual' requires bias_correction=True"
 
 
 # modes in which the permutation is renewed together with the selection (token_sparse.py:984); an update
@@ -382,17 +389,60 @@ class TokenSparseCache:
         self.layer_t = layer_t             # normalised depth in [0, 1] for adaptive_layers, else None
         self._step_count = 0
         self._cached_lse = None
-        self._cached_indices = None
-        self._cached_lengths = None
+        # indices, tile counts and residual live in slots that can park them in pinned host memory (residency.py)
+        from mcsparse_b200.kernels.flash_mcsa.residency import OffloadSlot
+        old = getattr(self, "_slots", None)
+        if old is not None:
+            for sl in old:
+                sl.clear()
+        self._idx, self._len, self._res = old if old is not None else (OffloadSlot(), OffloadSlot(), OffloadSlot())
+        self._slots = (self._idx, self._len, self._res)
         self._cached_perm = None
-        self._cached_residual = None
         self._perm_generation = 0          # advances on every permutation refresh
         self._residual_perm_gen = None     # generation the residual was computed under
         self._cached_len = None
 
+    # the three cached tensors as plain attributes: reading one makes it available on the current stream
+    @property
+    def _cached_indices(self):
+        return self._idx.get()
+
+    @_cached_indices.setter
+    def _cached_indices(self, t):
+        self._idx.store(t, offload=self.config.offload_indices)
+
+    @property
+    def _cached_lengths(self):
+        return self._len.get()
+
+    @_cached_lengths.setter
+    def _cached_lengths(self, t):
+        self._len.store(t, offload=self.config.offload_indices)
+
+    @property
+    def _cached_residual(self):
+        return self._res.get()
+
+    @_cached_residual.setter
+    def _cached_residual(self, t):
+        self._res.store(t, offload=self.config.cache_offload == 'residual')
+
     @property
     def has_cache(self) -> bool:
-        return self._cached_indices is not None
+        return self._idx.present
+
+    def prefetch(self) -> None:
+        """Start bringing offloaded tensors back if the coming use is a reuse step (token_sparse.py:340-361, :425-452)."""
+        if self.mode != 'reuse':
+            return
+        self._idx.prefetch()
+        self._len.prefetch()
+        if self.config.bias_correction and self._residual_perm_gen == self._perm_generation:
+            self._res.prefetch()
+
+    def offload_stats(self) -> dict:
+        return {"idx_prefetch_hit": self._idx.hits, "idx_prefetch_miss": self._idx.misses,
+                "res_prefetch_hit": self._res.hits, "res_prefetch_miss": self._res.misses}
 
     @property
     def mode(self) -> str:
@@ -420,7 +470,7 @@ class TokenSparseCache:
 
     def residual_if_valid(self):
         """The cached residual, unless it belongs to an older permutation (token_sparse.py:505-521)."""
-        if self._cached_residual is None:
+        if not self._res.present:
             return None
         if self.config.pca_reorder and self._residual_perm_gen != self._perm_generation:
             self._cached_residual = None
@@ -566,6 +616,8 @@ class TokenSparseContext:
         return self.caches[li]
 
     def forward(self, li: int, q, k, v, scale: Optional[float] = None, out_peers=None):
+        if self.config.offload_prefetch_ahead and li + 1 < len(self.caches):
+            self.caches[li + 1].prefetch()              # comes back under this layer's kernels
         if li in self.config.full_layers:
             return dense_attention_with_lse(q, k, v, scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))[0]
         return self.backend.forward(self.cache(li), q, k, v, scale, out_peers=out_peers)
@@ -573,6 +625,8 @@ class TokenSparseContext:
     def step(self) -> None:
         for c in self.caches:
             c.step()
+        if self.caches and self.config.offload_prefetch_ahead:
+            self.caches[0].prefetch()                   # the first layer of the next step has no layer in front of it
         # once per denoising step, without synchronising: did any kernel report an expired wait?
         if self.caches and torch.cuda.is_available():
             _lib.poll_status(torch.cuda.current_device(), "TokenSparseContext.step")
@@ -580,3 +634,11 @@ class TokenSparseContext:
     def reset(self) -> None:
         for c in self.caches:
             c.reset()
+
+    def offload_stats(self) -> dict:
+        """Prefetch hits and misses over all layers: a miss is a use that had to copy on its own stream."""
+        out = {"idx_prefetch_hit": 0, "idx_prefetch_miss": 0, "res_prefetch_hit": 0, "res_prefetch_miss": 0}
+        for c in self.caches:
+            for k, v in c.offload_stats().items():
+                out[k] += v
+        return out

@@ -120,3 +120,39 @@ def test_plain_calibrate_returns_sparse_output(cuda_device):
     ref, _ = gather_attn_ref(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), cache._cached_indices.cpu())
     mx, mr = error_metrics(out.transpose(1, 2), ref)
     assert mx < 2e-2 and mr < 1e-2, (mx, mr)
+
+
+def test_offloaded_metadata_gives_the_same_results(cuda_device):
+    """Indices and residual parked in pinned host memory and prefetched one layer ahead (the reference's
+    offload_indices / cache_offload='residual', token_sparse.py:313-487): bit-identical outputs over anchor and reuse
+    steps of a three-layer context, every use after the anchor step served by a prefetch."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    B, H, L, D, layers, steps = 1, 2, 1500, 128, 3, 4
+    dev = cuda_device
+    inputs = [[tuple(t.to(dev) for t in _qkv(B, H, L, D, 10 * s + li)) for li in range(layers)] for s in range(steps)]
+
+    def run(**kw):
+        cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], sink_ranges=[(0, 4)], bias_correction=True, pca_reorder=True,
+                                pca_pow_iters=4, **kw)
+        ctx = TokenSparseContext(cfg, num_layers=layers)
+        outs = []
+        for s in range(steps):
+            for li in range(layers):
+                outs.append(ctx.forward(li, *inputs[s][li]).clone())
+            ctx.step()
+        torch.cuda.synchronize()
+        return outs, ctx
+
+    base, _ = run()
+    off, ctx = run(offload_indices=True, cache_offload="residual")
+    assert all(torch.equal(a, b) for a, b in zip(base, off))
+    for c in ctx.caches:
+        assert c._idx.offloaded and c._res.offloaded and c._idx.gpu is None       # nothing of it stays in HBM between uses
+    st = ctx.offload_stats()
+    uses = layers * (steps - 1)
+    assert st["idx_prefetch_hit"] + st["idx_prefetch_miss"] == uses and st["res_prefetch_hit"] + st["res_prefetch_miss"] == uses
+    assert st["idx_prefetch_miss"] == 0 and st["res_prefetch_miss"] == 0, st
+    # without prefetching every use is a miss (a copy on the consuming stream), still the same numbers
+    off0, ctx0 = run(offload_indices=True, cache_offload="residual", offload_prefetch_ahead=0)
+    assert all(torch.equal(a, b) for a, b in zip(base, off0))
+    assert ctx0.offload_stats()["idx_prefetch_hit"] == 0 and ctx0.offload_stats()["idx_prefetch_miss"] == uses
