@@ -834,7 +834,7 @@ def run_fp8(args):
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / n_e2e
-    peak = _fp8_dense_peak(dev)
+    peak = _fp8_dense_peak(dev, sustain_s=0.2 if args.heads else 2.0)      # (a head subset is a profiling run: keep it short)
     bf16 = _peaks()
     achieved = flops / (ms * 1e-3) / 1e12
     line = {
@@ -877,6 +877,25 @@ def run_fp8(args):
         sys.exit(3)
 
 
+def run_layer(args):
+    """Secondary measurement on one GPU: the whole Ulysses DiT attention layer of the multi-GPU configuration
+    (``--heads N`` shrinks heads and hidden size together: the small case used for profiler captures)."""
+    import dataclasses
+    import torch
+    from mcsparse_b200 import _lib, synth
+    os.environ["MCSPARSE_B200_CHECK"] = "0"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = synth.C5
+    if args.heads:
+        shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
+    rec = _layer_bench(args, shape, 1, 0, dev, steps=max(2, args.steps))
+    _lib.check_status(dev, "layer bench")
+    print(json.dumps({"metric": "ulysses_layer_ms", "value": rec["ms"], "unit": "ms", "n_gpus": 1, "steps": rec["steps"],
+                      "warmup": 3, "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": rec["workload"]}, "layer": rec}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -902,9 +921,9 @@ def main():
     ap.add_argument("--no-layer", action="store_true", help="N > 1: skip the measurement of the whole layer")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
     ap.add_argument("--e2e-chunk", type=int, default=2, help="heads per chunk of the pipelined end-to-end step (one GPU)")
-    ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8"],
+    ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8", "layer"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
-                         "attn_fp8: the e4m3 variant at the long-video shape (1 GPU)")
+                         "attn_fp8: the e4m3 variant at the long-video shape (1 GPU); layer: the whole Ulysses DiT attention layer (1 GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -912,6 +931,8 @@ def main():
         run_anchor(args)
     elif args.workload == "attn_fp8":
         run_fp8(args)
+    elif args.workload == "layer":
+        run_layer(args)
     else:
         run_ours(args)
 
