@@ -96,6 +96,8 @@ typedef struct mcs_gather_attn_args {
   int32_t dtype;        /* MCS_DTYPE_* */
   float softmax_scale;  /* > 0; ignored for e4m3 (scale_qk_log2 carries it) */
   int32_t flags;        /* MCS_ATTN_* bits, 0 for the behaviour described above */
+  const uint16_t* gi16; /* with gi == NULL: the same indices in packed form, low 16 bits of every entry ... */
+  const uint32_t* gi_hi;/* ... and bit 16 as a bit plane, one 32-bit word per 32 consecutive entries (Sk <= 131,072) */
 } mcs_gather_attn_args;
 
 /* With perm != NULL: read the query rows through the permutation but keep out and lse in the permuted
@@ -243,6 +245,16 @@ int mcs_group_mass(const mcs_group_mass_args* args, void* stream);
  */
 int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink,
                     int64_t rows, int32_t L, int32_t k_total, void* stream);
+
+/*
+ * Packed form of an index tensor for sequences of up to 131,072 keys: n entries (a multiple of 128) become n 16-bit
+ * values and n / 32 words holding bit 16 of 32 consecutive entries each: 272 instead of 512 bytes per tile of 128.
+ * The attention entry points read this form directly (args->gi16 / gi_hi).  mcs_index_unpack17 is the inverse.
+ * No counterpart in the reference, which keeps int32 indices (639 MB per layer at its production shape,
+ * mcsparse/h3/token_sparse_dispatch.py:866-872) and moves them to host memory instead.
+ */
+int mcs_index_pack17(const int32_t* gi, int64_t n, uint16_t* lo, uint32_t* hi, void* stream);
+int mcs_index_unpack17(const uint16_t* lo, const uint32_t* hi, int64_t n, int32_t* gi, void* stream);
 
 /*
  * The same selection with a budget of its own for every row: row r gets the sinks plus its (k_rows[r] - n_sink)

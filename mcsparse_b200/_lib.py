@@ -36,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "mcs_group_mass",
     "mcs_topk_select",
     "mcs_topk_select_var",
+    "mcs_index_pack17",
+    "mcs_index_unpack17",
     "mcs_topp_count",
     "mcs_pddp_workspace_bytes",
     "mcs_pddp_start_vector_rows",
@@ -63,6 +65,7 @@ class GatherAttnArgs(C.Structure):
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
         ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
         ("softmax_scale", C.c_float), ("flags", C.c_int32),
+        ("gi16", C.c_void_p), ("gi_hi", C.c_void_p),
     ]
 
 
@@ -149,6 +152,10 @@ def lib() -> C.CDLL:
     L.mcs_topk_select_var.restype = C.c_int
     L.mcs_topk_select_var.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                       C.c_void_p, C.c_void_p]
+    L.mcs_index_pack17.restype = C.c_int
+    L.mcs_index_pack17.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.mcs_index_unpack17.restype = C.c_int
+    L.mcs_index_unpack17.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
     L.mcs_topp_count.restype = C.c_int
     L.mcs_topp_count.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_void_p]
     L.mcs_pddp_workspace_bytes.restype = C.c_int64

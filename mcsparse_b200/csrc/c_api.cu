@@ -59,7 +59,8 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
                                 bool dense, void* stream, bool negate = false) {
   if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
-  if (!dense && a->gi == nullptr) return MCS_ERR_NULL_POINTER;
+  if (!dense && a->gi == nullptr && (a->gi16 == nullptr || a->gi_hi == nullptr)) return MCS_ERR_NULL_POINTER;
+  if (a->gi16 != nullptr && a->Sk > (1 << 17)) return MCS_ERR_TOO_LARGE;        // packed indices carry 17 bits
   if (n_peers == 0 && a->out == nullptr) return MCS_ERR_NULL_POINTER;
   if (n_peers > 0) {
     if (out_peers == nullptr) return MCS_ERR_NULL_POINTER;
@@ -90,7 +91,8 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
 
   mcs::GatherAttnParams p{};
   p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out; p.lse = a->lse;
-  p.gi = a->gi; p.gl = a->gl; p.residual = a->residual; p.perm = a->perm;
+  p.gi = a->gi; p.gl = a->gl;
+  if (a->gi == nullptr) { p.gi16 = a->gi16; p.gi_hi = a->gi_hi; } p.residual = a->residual; p.perm = a->perm;
   p.scale_qk_log2 = a->scale_qk_log2; p.scale_v = a->scale_v; p.status = a->status;
   for (int i = 0; i < 3; ++i) {
     p.q_stride[i] = a->q_stride[i]; p.k_stride[i] = a->k_stride[i]; p.v_stride[i] = a->v_stride[i];
@@ -100,7 +102,7 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   p.M = (int)groups; p.gather_len = a->gather_len; p.group_rows = a->group_rows;
   if (dense) {
     p.dense = 1;
-    p.gi = nullptr;
+    p.gi = nullptr; p.gi16 = nullptr; p.gi_hi = nullptr;
     p.gather_len = (a->Sk + 127) / 128 * 128;       // every key tile of the sequence
   }
   if (negate && a->residual == nullptr) return MCS_ERR_NULL_POINTER;
@@ -223,6 +225,18 @@ int mcs_topk_select(const float* scores, int32_t* out, const int32_t* sinks, int
   if (rows == 0) return 0;
   mcs::TopkParams p{scores, out, sinks, (long long)rows, L, k_total, n_sink, nullptr};
   return mcs::launch_topk_select(p, static_cast<cudaStream_t>(stream));
+}
+
+int mcs_index_pack17(const int32_t* gi, int64_t n, uint16_t* lo, uint32_t* hi, void* stream) {
+  if (gi == nullptr || lo == nullptr || hi == nullptr) return MCS_ERR_NULL_POINTER;
+  if (n < 0 || n % 128 != 0) return MCS_ERR_BAD_SHAPE;
+  return mcs::launch_index_pack17(gi, (long long)n, lo, hi, static_cast<cudaStream_t>(stream));
+}
+
+int mcs_index_unpack17(const uint16_t* lo, const uint32_t* hi, int64_t n, int32_t* gi, void* stream) {
+  if (gi == nullptr || lo == nullptr || hi == nullptr) return MCS_ERR_NULL_POINTER;
+  if (n < 0 || n % 128 != 0) return MCS_ERR_BAD_SHAPE;
+  return mcs::launch_index_unpack17(lo, hi, (long long)n, gi, static_cast<cudaStream_t>(stream));
 }
 
 int mcs_topk_select_var(const float* scores, int32_t* out, const int32_t* sinks, int32_t n_sink, int64_t rows, int32_t L,

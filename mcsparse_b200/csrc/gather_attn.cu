@@ -176,7 +176,7 @@ __device__ __forceinline__ Item decode_item(const GatherAttnParams& p, int item)
   const int max_tiles = p.gather_len / kTileN;
   it.T = max_tiles;
   if (p.gl != nullptr) it.T = min(max(p.gl[item], 1), max_tiles);
-  it.gi = p.dense ? nullptr : p.gi + (size_t)item * p.gather_len;
+  it.gi = (p.dense || p.gi == nullptr) ? nullptr : p.gi + (size_t)item * p.gather_len;
   return it;
 }
 
@@ -471,8 +471,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         }
       }
       if (!kDense && item + (int)gridDim.x < n_items) {
-        const uint8_t* gin = reinterpret_cast<const uint8_t*>(p.gi + (size_t)(item + gridDim.x) * p.gather_len);
-        const int bytes = p.gather_len * 4;
+        // (packed indices: 2 bytes per entry; their bit planes are 1/16 of that and are left to the loads themselves)
+        const size_t next = (size_t)(item + gridDim.x) * p.gather_len;
+        const uint8_t* gin = p.gi16 != nullptr ? reinterpret_cast<const uint8_t*>(p.gi16 + next) : reinterpret_cast<const uint8_t*>(p.gi + next);
+        const int bytes = p.gather_len * (p.gi16 != nullptr ? 2 : 4);
         for (int off = (pw * 32 + lane) * 128; off < bytes; off += kProducerThreads * 128) prefetch_l2(gin + off);
       }
       if (ic >= 2) ok = ok && mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((ic >> 1) - 1) & 1, p.status, 22) &&
@@ -488,6 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
     struct Cur {
       int item, ic, t, T, b, h;
       const int32_t* gi;     // this thread's entry of tile 0
+      size_t ioff;           // the same as an offset into the index tensor (packed form)
       const uint8_t* kv;     // K or V base of (b, h) + chunk offset of this lane
     };
     const bool tma_leader = elect_one();
@@ -526,17 +529,27 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
       c.b = it.b;
       c.h = it.h;
       c.gi = kDense ? nullptr : it.gi + my_row;
+      c.ioff = (size_t)c.item * p.gather_len + my_row;
       c.kv = reinterpret_cast<const uint8_t*>(tensor) + kEs * ((size_t)it.b * stride[0] + (size_t)it.h * stride[2]) + chunk_off;
     };
     // dense mode: the "selected" tokens of tile t are simply t*128 .. t*128+127 (rows beyond the end are
     // clamped here and masked in the softmax)
-    auto load_idx = [&](const Cur& c) { return kDense ? c.t * kTileN + my_row : __ldg(c.gi + c.t * kTileN); };
+    auto load_idx = [&](const Cur& c) -> int {
+      if (kDense) return c.t * kTileN + my_row;
+      if (p.gi16 != nullptr) {
+        // 17-bit indices: the low 16 bits as an array of their own, bit 16 in a bit plane (one word per 32 entries)
+        const size_t o = c.ioff + (size_t)c.t * kTileN;
+        const uint32_t lo = __ldg(p.gi16 + o), hi = (__ldg(p.gi_hi + (o >> 5)) >> (o & 31)) & 1u;
+        return static_cast<int>(lo | (hi << 16));
+      }
+      return __ldg(c.gi + c.t * kTileN);
+    };
 
     // Fill order = consumption order of the MMA warp: K(0), then per tile g: K(g+1), V(g),
     // where g+1 may belong to the next work item (its Q is requested just before its K(0)).
     // The indices of the next K tile are fetched one step ahead of their use.
     if (blockIdx.x < n_items) {
-      Cur kc{static_cast<int>(blockIdx.x), 0, 0, 0, 0, 0, nullptr, nullptr}, vc = kc;
+      Cur kc{static_cast<int>(blockIdx.x), 0, 0, 0, 0, 0, nullptr, 0, nullptr}, vc = kc;
       set_item(kc, p.k, p.k_stride);
       set_item(vc, p.v, p.v_stride);
       enter_item(kc.item, kc.ic);

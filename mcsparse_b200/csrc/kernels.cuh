@@ -12,6 +12,8 @@ struct GatherAttnParams {
   void* out;
   float* lse;
   const int32_t* gi;
+  const uint16_t* gi16;        // packed indices (instead of gi): low 16 bits ...
+  const uint32_t* gi_hi;       // ... and bit 16 as a bit plane, one word per 32 entries
   const int32_t* gl;
   const void* residual;
   const int64_t* perm;
@@ -107,6 +109,8 @@ struct TopkParams {
   int L, k_total, n_sink;
   const int32_t* k_rows;  // optional per-row budgets (sinks included), clamped to [n_sink, k_total]; entries beyond are zeroed
 };
+int launch_index_pack17(const int32_t* gi, long long n, uint16_t* lo, uint32_t* hi, cudaStream_t stream);
+int launch_index_unpack17(const uint16_t* lo, const uint32_t* hi, long long n, int32_t* gi, cudaStream_t stream);
 int launch_topp_count(const float* scores, const int32_t* sinks, int n_sink, long long rows, int L, float topp, int32_t* counts,
                       cudaStream_t stream);
 

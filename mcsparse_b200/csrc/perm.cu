@@ -44,4 +44,42 @@ int launch_perm_rows(const void* x, void* out, const long long* perm, int BH, in
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
+namespace {
+// 17-bit token indices (sequences of up to 131,072 keys) as 16 bits + one bit: 272 instead of 512 bytes per tile of 128.
+__global__ void __launch_bounds__(256) index_pack17_kernel(const int32_t* __restrict__ gi, long long n, uint16_t* __restrict__ lo,
+                                                           uint32_t* __restrict__ hi) {
+  const long long i0 = ((long long)blockIdx.x * 256 + threadIdx.x);
+  const long long step = (long long)gridDim.x * 256;
+  for (long long i = i0; i < n + 31; i += step) {                  // whole warps: n is a multiple of 32
+    const int v = i < n ? gi[i] : 0;
+    const unsigned b = __ballot_sync(0xffffffffu, (v >> 16) & 1);
+    if (i < n) {
+      lo[i] = (uint16_t)(v & 0xFFFF);
+      if ((threadIdx.x & 31) == 0) hi[i >> 5] = b;
+    }
+  }
+}
+__global__ void __launch_bounds__(256) index_unpack17_kernel(const uint16_t* __restrict__ lo, const uint32_t* __restrict__ hi, long long n,
+                                                             int32_t* __restrict__ gi) {
+  const long long step = (long long)gridDim.x * 256;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n; i += step)
+    gi[i] = (int)lo[i] | (int)(((hi[i >> 5] >> (i & 31)) & 1u) << 16);
+}
+}  // namespace
+
+int launch_index_pack17(const int32_t* gi, long long n, uint16_t* lo, uint32_t* hi, cudaStream_t stream) {
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  index_pack17_kernel<<<(unsigned)blocks, 256, 0, stream>>>(gi, n, lo, hi);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+int launch_index_unpack17(const uint16_t* lo, const uint32_t* hi, long long n, int32_t* gi, cudaStream_t stream) {
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  index_unpack17_kernel<<<(unsigned)blocks, 256, 0, stream>>>(lo, hi, n, gi);
+  return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
 }  // namespace mcs

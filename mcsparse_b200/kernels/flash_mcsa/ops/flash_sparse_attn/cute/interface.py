@@ -34,6 +34,57 @@ from mcsparse_b200 import _lib
 _TILE_N = 128
 
 
+class PackedIndices:
+    """An index tensor (B, H, M, gather_len) for sequences of up to 131,072 keys in 17-bit form: ``lo`` holds the low 16
+    bits of every entry (int16 storage), ``hi`` bit 16 of 32 consecutive entries per int32 word: 272 instead of 512
+    bytes per tile of 128.  The attention kernels read this form directly; pass it wherever ``gather_kv_indices`` is
+    expected.  (The reference keeps int32 indices and offloads them to host memory; there is no such format there.)"""
+
+    def __init__(self, lo: torch.Tensor, hi: torch.Tensor, shape):
+        self.lo, self.hi, self.shape = lo, hi, tuple(shape)
+
+    @property
+    def device(self):
+        return self.lo.device
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.lo.is_cuda
+
+    def nbytes(self) -> int:
+        return self.lo.numel() * 2 + self.hi.numel() * 4
+
+    @staticmethod
+    def pack(gi: torch.Tensor) -> "PackedIndices":
+        if gi.dtype != torch.int32 or not gi.is_cuda or gi.shape[-1] % 128 != 0:
+            raise ValueError("pack() takes an int32 CUDA tensor whose last dimension is a multiple of 128")
+        gi = gi.contiguous()
+        n = gi.numel()
+        lo = torch.empty(gi.shape, dtype=torch.int16, device=gi.device)
+        hi = torch.empty(n // 32, dtype=torch.int32, device=gi.device)
+        stream = torch.cuda.current_stream(gi.device).cuda_stream
+        _lib.raise_on_error(_lib.lib().mcs_index_pack17(gi.data_ptr(), n, lo.data_ptr(), hi.data_ptr(), stream), "mcs_index_pack17")
+        return PackedIndices(lo, hi, gi.shape)
+
+    def unpack(self) -> torch.Tensor:
+        gi = torch.empty(self.shape, dtype=torch.int32, device=self.lo.device)
+        stream = torch.cuda.current_stream(self.lo.device).cuda_stream
+        _lib.raise_on_error(_lib.lib().mcs_index_unpack17(self.lo.data_ptr(), self.hi.data_ptr(), gi.numel(), gi.data_ptr(), stream),
+                            "mcs_index_unpack17")
+        return gi
+
+    def __getitem__(self, key):
+        # head slices are what the callers take (e.g. gi[:, h0:h1]); anything else goes through the int32 form
+        if (isinstance(key, tuple) and len(key) == 2 and key[0] == slice(None) and isinstance(key[1], slice)
+                and key[1].step in (None, 1)):
+            B, H, M, K = self.shape
+            h0, h1, _ = key[1].indices(H)
+            if B == 1:
+                per = M * K
+                return PackedIndices(self.lo[:, h0:h1], self.hi.view(B, H, per // 32)[:, h0:h1].reshape(-1), (B, h1 - h0, M, K))
+        raise TypeError("only gi[:, h0:h1] on a batch-1 tensor can be sliced in packed form; unpack() first")
+
+
 def maybe_contiguous(x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return x.contiguous() if x is not None and x.stride(-1) != 1 else x
 
@@ -101,9 +152,15 @@ def _shape_checks(q, k, v):
 
 def _index_checks(gather_kv_indices, gather_kv_lengths, batch_size, num_head, num_m_blocks, seqlen_k):
     gather_len = gather_kv_indices.shape[-1]
-    if gather_kv_indices.dtype != torch.int32:
+    packed = isinstance(gather_kv_indices, PackedIndices)
+    if packed:
+        if seqlen_k > (1 << 17):
+            raise ValueError("packed indices carry 17 bits: seqlen_k must be <= 131072")
+        if not gather_kv_indices.lo.is_contiguous() or not gather_kv_indices.hi.is_contiguous():
+            gather_kv_indices = PackedIndices(gather_kv_indices.lo.contiguous(), gather_kv_indices.hi.contiguous(), gather_kv_indices.shape)
+    elif gather_kv_indices.dtype != torch.int32:
         raise TypeError("gather_kv_indices must be int32")
-    if gather_kv_indices.stride(-1) != 1:
+    elif gather_kv_indices.stride(-1) != 1:
         raise ValueError("gather_kv_indices must be contiguous in the last dimension")
     if gather_len % _TILE_N != 0:
         raise ValueError(f"gather_len must be divisible by {_TILE_N}, got {gather_len}")
@@ -122,7 +179,7 @@ def _index_checks(gather_kv_indices, gather_kv_lengths, batch_size, num_head, nu
                 f"gather_kv_lengths must have shape {expected[:3]}, got {tuple(gather_kv_lengths.shape)}")
         if not gather_kv_lengths.is_contiguous():
             gather_kv_lengths = gather_kv_lengths.contiguous()
-    if not gather_kv_indices.is_contiguous():
+    if not packed and not gather_kv_indices.is_contiguous():
         gather_kv_indices = gather_kv_indices.contiguous()
     return gather_kv_indices, gather_kv_lengths, gather_len
 
@@ -172,7 +229,11 @@ def _fill_args(q, k, v, out, lse, gi, gl, residual, perm, gather_len, group_rows
                scale_qk_log2=None, scale_v=None) -> "_lib.GatherAttnArgs":
     a = _lib.GatherAttnArgs()
     a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
-    a.lse, a.gi, a.gl = _ptr(lse), gi.data_ptr(), _ptr(gl)
+    if isinstance(gi, PackedIndices):
+        a.gi, a.gi16, a.gi_hi = None, gi.lo.data_ptr(), gi.hi.data_ptr()
+    else:
+        a.gi = gi.data_ptr()
+    a.lse, a.gl = _ptr(lse), _ptr(gl)
     a.residual, a.perm = _ptr(residual), _ptr(perm)
     a.scale_qk_log2, a.scale_v = _ptr(scale_qk_log2), _ptr(scale_v)
     a.status = _lib.status_word(q.device).data_ptr()

@@ -341,6 +341,7 @@ class TokenSparseConfig:
     offload_indices: bool = False          # keep the indices in pinned host memory between uses (reference default: True)
     cache_offload: str = 'none'            # 'residual': the same for the bias-correction residual
     offload_prefetch_ahead: int = 1        # layers ahead of its use at which an offloaded tensor starts to come back
+    compact_indices: bool = False          # keep the cached indices in the packed 17-bit form (sequences up to 131,072 keys)
 
     def __post_init__(self):
         assert 0 < self.topk <= 1.0
@@ -373,6 +374,7 @@ class TokenSparseConfig:
         assert self.offload_prefetch_ahead in (0, 1), "offload_prefetch_ahead only supports 0 or 1"
         if self.cache_offload == 'residual':
             assert self.bias_correction, "cache_offload='residual' requires bias_correction=True"
+        assert not (self.compact_indices and self.offload_indices), "compact_indices keeps the indices in HBM; choose one of the two"
 
 
 # modes in which the permutation is renewed together with the selection (token_sparse.py:984); an update
@@ -409,6 +411,10 @@ class TokenSparseCache:
 
     @_cached_indices.setter
     def _cached_indices(self, t):
+        if self.config.compact_indices and isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int32 \
+                and self._cached_len is not None and self._cached_len[1] <= (1 << 17):
+            from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import PackedIndices
+            t = PackedIndices.pack(t)              # 272 instead of 512 bytes per tile; the attention kernel reads it as it is
         self._idx.store(t, offload=self.config.offload_indices)
 
     @property

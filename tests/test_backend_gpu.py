@@ -156,3 +156,28 @@ def test_offloaded_metadata_gives_the_same_results(cuda_device):
     off0, ctx0 = run(offload_indices=True, cache_offload="residual", offload_prefetch_ahead=0)
     assert all(torch.equal(a, b) for a, b in zip(base, off0))
     assert ctx0.offload_stats()["idx_prefetch_hit"] == 0 and ctx0.offload_stats()["idx_prefetch_miss"] == uses
+
+
+def test_compact_index_cache(cuda_device):
+    """``compact_indices=True``: the cache holds the packed 17-bit indices and every later step reads them in place."""
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import PackedIndices
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    B, H, L, D = 1, 2, 1500, 128
+    dev = cuda_device
+    steps = [tuple(t.to(dev) for t in _qkv(B, H, L, D, 30 + s)) for s in range(3)]
+
+    def run(**kw):
+        cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], sink_ranges=[(0, 4)], bias_correction=True, pca_reorder=True,
+                                pca_pow_iters=4, **kw)
+        ctx = TokenSparseContext(cfg, num_layers=1)
+        outs = []
+        for s in range(3):
+            outs.append(ctx.forward(0, *steps[s]).clone())
+            ctx.step()
+        return outs, ctx
+
+    base, ctx0 = run()
+    comp, ctx1 = run(compact_indices=True)
+    assert all(torch.equal(a, b) for a, b in zip(base, comp))
+    gi = ctx1.caches[0]._cached_indices
+    assert isinstance(gi, PackedIndices) and torch.equal(gi.unpack(), ctx0.caches[0]._cached_indices)

@@ -178,3 +178,34 @@ def test_residual_minus_attention(cuda_device):
     with pytest.raises(ValueError):
         flash_attn_gather_kv_func(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), gi.to(cuda_device),
                                   residual_minus_attention=True)
+
+
+@pytest.mark.parametrize("Sk", [3000, 98280])
+def test_packed_indices_give_the_same_bits(cuda_device, Sk):
+    """17-bit packed indices (16 bits + a bit plane) read by the kernel directly: same output as int32 indices."""
+    from mcsparse_b200 import synth
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import PackedIndices, flash_attn_gather_kv_func
+    dev = cuda_device
+    B, H, Sq, D, KS = 1, 3, 900, 128, 384
+    g = torch.Generator().manual_seed(Sk)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(B, Sk, H, D, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(B, Sk, H, D, generator=g).to(torch.bfloat16).to(dev)
+    M = math.ceil(Sq / 128)
+    gi = synth.random_sorted_indices(B, H, M, KS, Sk, seed=1, device=dev)
+    if Sk > 65536:
+        assert int(gi.max()) > 65535                                   # bit 16 is in use
+    gl = torch.randint(1, 4, (B, H, M), generator=g, dtype=torch.int32).to(dev)
+    packed = PackedIndices.pack(gi)
+    assert packed.nbytes() * 512 == gi.numel() * 4 * 272 and torch.equal(packed.unpack(), gi)
+    want, _ = flash_attn_gather_kv_func(q, k, v, gi, gather_kv_lengths=gl)
+    got, _ = flash_attn_gather_kv_func(q, k, v, packed, gather_kv_lengths=gl)
+    assert torch.equal(got, want)
+    # a head slice of the packed form, as the chunked callers take it
+    got1, _ = flash_attn_gather_kv_func(q[:, :, 1:3], k[:, :, 1:3], v[:, :, 1:3], packed[:, 1:3], gather_kv_lengths=gl[:, 1:3].contiguous())
+    assert torch.equal(got1, want[:, :, 1:3])
+    if Sk <= 65536:
+        return
+    with pytest.raises(ValueError):
+        big_k = torch.zeros(B, (1 << 17) + 128, H, D, dtype=torch.bfloat16, device=dev)
+        flash_attn_gather_kv_func(q, big_k, big_k, packed)
