@@ -177,6 +177,7 @@ int mcs_qkv_norm_rope_scatter(const mcs_qkv_epilogue_args* a, void* stream) {
   if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
   if (a->grid_f < 1 || a->grid_h < 1 || a->grid_w < 1 || a->pairs_t < 0 || a->pairs_h < 0 || a->pairs_t + a->pairs_h > a->D / 2)
     return MCS_ERR_BAD_SHAPE;
+  if ((int64_t)a->grid_f * a->grid_h * a->grid_w > 0x7fffffffLL) return MCS_ERR_TOO_LARGE;
   if (a->token0 + a->rows > (int64_t)a->grid_f * a->grid_h * a->grid_w) return MCS_ERR_BAD_SHAPE;
   if (a->src_row_stride < (int64_t)a->n_seg * a->D || a->src_row_stride % 8 || !aligned16(a->src)) return MCS_ERR_BAD_ALIGNMENT;
   if (!(a->eps >= 0.f) || !std::isfinite(a->eps)) return MCS_ERR_BAD_SCALE;

@@ -51,82 +51,91 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   else return pack_bf16x2(lo, hi);
 }
 
-// D = 128: sixteen lanes per (token, slice), eight elements (four rotation pairs) per lane.  D = 64: the same
-// sixteen lanes with four elements each (8-byte accesses).
+// Sixteen lanes (a half-warp) per token: the half-warp computes the token's grid position and fetches its rotation
+// factors and the RMSNorm weights once, then walks the token's head slices two at a time (both 16-byte loads issued
+// before either slice is touched).  D = 128: eight elements (four rotation pairs) per lane; D = 64: four elements.
 template <int D, bool kFp16>
 __global__ void __launch_bounds__(kThreads) qkv_norm_rope_scatter_kernel(const QkvEpilogueParams p, const __grid_constant__ SegTable seg) {
   constexpr int kEl = D / kLanesPerSlice;                  // elements per lane: 8 or 4
   constexpr int kPairs = kEl / 2;
-  constexpr int kUnroll = 4;                               // slices in flight per half-warp: the kernel is bound by memory latency
+  constexpr int kUnroll = 2;
   const int lane16 = threadIdx.x & 15;
-  const long long slices = (long long)p.rows * p.n_seg;
-  const long long step = (long long)gridDim.x * (kThreads / kLanesPerSlice);
-  const int hw = p.grid_h * p.grid_w;
   const uint32_t half_mask = 0xFFFFu << (threadIdx.x & 16);
-  for (long long sl0 = (long long)blockIdx.x * (kThreads / kLanesPerSlice) + (threadIdx.x >> 4); sl0 < slices; sl0 += step * kUnroll) {
-    uint32_t w[kUnroll][kEl / 2];
-    long long row[kUnroll];
-    int seg_i[kUnroll];
-    // all loads first
+  const int hw = p.grid_h * p.grid_w;
+  const int n_seg = p.n_seg;
+  // weights of this lane's elements
+  float gq[kEl], gk[kEl];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const long long sl = sl0 + (long long)u * step;
-      seg_i[u] = -1;
-      if (sl < slices) {
-        row[u] = sl / p.n_seg;
-        seg_i[u] = (int)(sl - row[u] * p.n_seg);
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src) + 2 * (row[u] * p.src_row_stride + (long long)seg_i[u] * D + lane16 * kEl);
-        if constexpr (kEl == 8) {
-          const uint4 v = *reinterpret_cast<const uint4*>(src);
-          w[u][0] = v.x; w[u][1] = v.y; w[u][2] = v.z; w[u][3] = v.w;
-        } else {
-          const uint2 v = *reinterpret_cast<const uint2*>(src);
-          w[u][0] = v.x; w[u][1] = v.y;
-        }
-      }
+  for (int j = 0; j < kEl; ++j) {
+    gq[j] = __ldg(p.gamma_q + lane16 * kEl + j);
+    gk[j] = __ldg(p.gamma_k + lane16 * kEl + j);
+  }
+  const long long step = (long long)gridDim.x * (kThreads / kLanesPerSlice);
+  for (long long row = (long long)blockIdx.x * (kThreads / kLanesPerSlice) + (threadIdx.x >> 4); row < p.rows; row += step) {
+    // position of the token on the (frames, rows, columns) grid and the (cos, sin) of this lane's rotation pairs:
+    // pairs [0, n_t) turn with the frame index, [n_t, n_t + n_h) with the grid row, the rest with the grid column
+    const unsigned tok = (unsigned)(p.token0 + row);       // (the C ABI checks that the grid has fewer than 2^31 tokens)
+    const int f = (int)(tok / (unsigned)hw);
+    const int rem = (int)(tok - (unsigned)f * (unsigned)hw);
+    const int y = rem / p.grid_w;
+    const int xw = rem - y * p.grid_w;
+    float2 cs[kPairs];
+#pragma unroll
+    for (int j = 0; j < kPairs; ++j) {
+      const int pr = lane16 * kPairs + j;
+      const int pos = pr < p.pairs_t ? f : (pr < p.pairs_t + p.pairs_h ? p.grid_f + y : p.grid_f + p.grid_h + xw);
+      cs[j] = __ldg(p.rope_cs + (size_t)pos * (D / 2) + pr);
     }
+    const uint8_t* src_row = reinterpret_cast<const uint8_t*>(p.src) + 2 * (row * p.src_row_stride + lane16 * kEl);
+    const long long drow = p.row0 + row;
+#pragma unroll 1
+    for (int s0 = 0; s0 < n_seg; s0 += kUnroll) {
+      uint32_t w[kUnroll][kEl / 2];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      if (seg_i[u] < 0) continue;                          // (uniform over the half-warp)
-      const int s = seg_i[u];
-      const int kind = seg.kind[s];
-      if (kind != 2) {
-        float x[kEl];
-#pragma unroll
-        for (int j = 0; j < kPairs; ++j) {
-          const float2 f = unpack2<kFp16>(w[u][j]);
-          x[2 * j] = f.x;
-          x[2 * j + 1] = f.y;
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < kEl; ++j) ss = fmaf(x[j], x[j], ss);
-        // the sixteen lanes of a slice are a half-warp: xor offsets below 16 stay inside it, and the mask names
-        // only that half (the other half may hold a value slice, or nothing at the end of the grid)
-#pragma unroll
-        for (int off = 8; off >= 1; off >>= 1) ss += __shfl_xor_sync(half_mask, ss, off);
-        const float rinv = rsqrtf(ss * (1.0f / D) + p.eps);
-        const float* g = (kind == 0 ? p.gamma_q : p.gamma_k) + lane16 * kEl;
-        // position of the token on the (frames, rows, columns) grid
-        const long long tok = p.token0 + row[u];
-        const int f = (int)(tok / hw);
-        const int rem = (int)(tok - (long long)f * hw);
-        const int y = rem / p.grid_w;
-        const int xw = rem - y * p.grid_w;
-#pragma unroll
-        for (int j = 0; j < kPairs; ++j) {
-          const int pr = lane16 * kPairs + j;              // rotation pair inside the slice
-          // pairs [0, n_t) turn with the frame index, [n_t, n_t + n_h) with the row, the rest with the column
-          const int pos = pr < p.pairs_t ? f : (pr < p.pairs_t + p.pairs_h ? p.grid_f + y : p.grid_f + p.grid_h + xw);
-          const float2 cs = __ldg(p.rope_cs + (long long)pos * (D / 2) + pr);
-          const float a = x[2 * j] * rinv * g[2 * j];
-          const float b = x[2 * j + 1] * rinv * g[2 * j + 1];
-          w[u][j] = pack2<kFp16>(a * cs.x - b * cs.y, a * cs.y + b * cs.x);
+      for (int u = 0; u < kUnroll; ++u) {
+        if (s0 + u < n_seg) {
+          const uint8_t* src = src_row + 2 * (size_t)(s0 + u) * D;
+          if constexpr (kEl == 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src);
+            w[u][0] = v.x; w[u][1] = v.y; w[u][2] = v.z; w[u][3] = v.w;
+          } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(src);
+            w[u][0] = v.x; w[u][1] = v.y;
+          }
         }
       }
-      uint8_t* dst = seg.dst[s] + 2 * ((p.row0 + row[u]) * seg.dst_row_stride[s] + lane16 * kEl);
-      if constexpr (kEl == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
-      else *reinterpret_cast<uint2*>(dst) = make_uint2(w[u][0], w[u][1]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int s = s0 + u;
+        if (s >= n_seg) break;                               // (uniform over the half-warp)
+        const int kind = seg.kind[s];
+        if (kind != 2) {
+          float x[kEl];
+#pragma unroll
+          for (int j = 0; j < kPairs; ++j) {
+            const float2 fv = unpack2<kFp16>(w[u][j]);
+            x[2 * j] = fv.x;
+            x[2 * j + 1] = fv.y;
+          }
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < kEl; ++j) ss = fmaf(x[j], x[j], ss);
+          // the sixteen lanes of a slice are a half-warp: xor offsets below 16 stay inside it, and the mask names
+          // only that half (the other half works on another token, or on nothing at the end of the grid)
+#pragma unroll
+          for (int off = 8; off >= 1; off >>= 1) ss += __shfl_xor_sync(half_mask, ss, off);
+          const float rinv = rsqrtf(ss * (1.0f / D) + p.eps);
+#pragma unroll
+          for (int j = 0; j < kPairs; ++j) {
+            const float a = x[2 * j] * rinv * (kind == 0 ? gq[2 * j] : gk[2 * j]);
+            const float b = x[2 * j + 1] * rinv * (kind == 0 ? gq[2 * j + 1] : gk[2 * j + 1]);
+            w[u][j] = pack2<kFp16>(a * cs[j].x - b * cs[j].y, a * cs[j].y + b * cs[j].x);
+          }
+        }
+        uint8_t* dst = seg.dst[s] + 2 * (drow * seg.dst_row_stride[s] + lane16 * kEl);
+        if constexpr (kEl == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(w[u][0], w[u][1], w[u][2], w[u][3]);
+        else *reinterpret_cast<uint2*>(dst) = make_uint2(w[u][0], w[u][1]);
+      }
     }
   }
 }
@@ -143,11 +152,10 @@ int launch_qkv_epilogue(const QkvEpilogueParams& p, void* const* dst, const long
     seg.dst_row_stride[i] = dst_row_stride[i];
     seg.kind[i] = kind[i];
   }
-  const long long slices = (long long)p.rows * p.n_seg;
   const long long per_block = kThreads / kLanesPerSlice;
-  long long blocks = (slices + per_block * 4 - 1) / (per_block * 4);          // four slices per half-warp and iteration
-  // memory- and link-bound: four CTAs of 256 threads per SM are plenty; grid-stride for the rest
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  // one half-warp per token; memory- and link-bound: eight CTAs of 256 threads per SM, grid-stride for the rest
+  long long blocks = (p.rows + per_block - 1) / per_block;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   if (p.D == 128) {
     if (fp16) qkv_norm_rope_scatter_kernel<128, true><<<(unsigned)blocks, kThreads, 0, stream>>>(p, seg);
     else qkv_norm_rope_scatter_kernel<128, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, seg);
