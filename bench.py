@@ -326,9 +326,14 @@ def _layer_bench(args, shape, world: int, rank: int, dev, steps: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0])
     fl = layer.flops(shape.topk)
+    # one more forward with timing events around every phase (rank 0's two streams), outside the timed region
+    _, spans = layer.traced_forward(x)
+    if world > 1:
+        dist.barrier()
     rec = {"workload": f"ulysses_layer_hidden{hidden}_H{H}_D{D}_L{L}_topk{shape.topk}", "n_gpus": world, "ms": ms,
            "tflops": fl["total"] / (ms * 1e-3) / 1e12, "gemm_flops": fl["gemm"], "attention_flops": fl["attention"],
            "head_chunks": layer.chunks, "steps": steps,
+           "timeline_ms_rank0": [[n, round(a, 3), round(b, 3)] for n, a, b in spans],
            "what": "QKV projection by head chunk (library GEMM) -> RMSNorm + RoPE-3D + peer-store exchange in one kernel per "
                    "chunk under the next chunk's GEMM -> sparse attention, rows stored into the owners' shards -> output projection"}
     if world == 1:

@@ -168,6 +168,39 @@ class UlyssesDiTAttentionLayer:
         self.s_comm = torch.cuda.Stream(device)
         self.gi = self.residual = self.perm = None
         self.attn_fn: Optional[Callable] = None
+        self._trace = None          # list of (name, start event, end event) while a traced forward runs
+
+    def _span(self, name: str, stream):
+        """Context manager that brackets the enclosed launches with two timing events when a trace is being taken."""
+        layer = self
+
+        class _Span:
+            def __enter__(self_inner):
+                if layer._trace is not None:
+                    self_inner.e0 = torch.cuda.Event(enable_timing=True)
+                    self_inner.e0.record(stream)
+
+            def __exit__(self_inner, *exc):
+                if layer._trace is not None:
+                    e1 = torch.cuda.Event(enable_timing=True)
+                    e1.record(stream)
+                    layer._trace.append((name, self_inner.e0, e1))
+                return False
+        return _Span()
+
+    def traced_forward(self, x: torch.Tensor):
+        """One forward with timing events around every phase.  Returns (output, [(name, start_ms, end_ms)]) with
+        times relative to the first launch: what runs under what on the two streams of this rank."""
+        self._trace = []
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record(torch.cuda.current_stream())
+        try:
+            out = self.forward(x)
+            torch.cuda.synchronize()
+            spans = [(n, t0.elapsed_time(a), t0.elapsed_time(b)) for n, a, b in self._trace]
+        finally:
+            self._trace = None
+        return out, sorted(spans, key=lambda r: r[1])
 
     # ------------------------------------------------------------------------------------------ metadata
     def set_metadata(self, gi: torch.Tensor, residual: Optional[torch.Tensor] = None, perm: Optional[torch.Tensor] = None):
@@ -210,15 +243,18 @@ class UlyssesDiTAttentionLayer:
         for c in range(self.chunks):
             if c >= len(self._y) and ev_read[c - len(self._y)] is not None:
                 main.wait_event(ev_read[c - len(self._y)])           # the epilogue has read the GEMM buffer about to be reused
-            y = self.project_chunk(x, c)
+            with self._span(f"qkv_gemm[{c}]", main):
+                y = self.project_chunk(x, c)
             ev_g = torch.cuda.Event()
             ev_g.record(main)
             with torch.cuda.stream(self.s_comm):
                 self.s_comm.wait_event(ev_g)
-                self.scatter_chunk(y, c)
+                with self._span(f"norm_rope_scatter[{c}]", self.s_comm):
+                    self.scatter_chunk(y, c)
                 ev_read[c] = torch.cuda.Event()
                 ev_read[c].record(self.s_comm)
-                self._order(self.flag, self.group)
+                with self._span(f"order[{c}]", self.s_comm):
+                    self._order(self.flag, self.group)
                 e = torch.cuda.Event()
                 e.record(self.s_comm)
                 ev_done.append(e)
@@ -235,17 +271,20 @@ class UlyssesDiTAttentionLayer:
                 main.wait_event(events[c])
             h0, h1 = c * self.hc, (c + 1) * self.hc
             q, k, v = self.local_qkv(c)
-            flash_attn_gather_kv_func(q, k, v, self.gi[:, h0:h1], residual=None if self.residual is None else self.residual[:, h0:h1],
-                                      perm=None if self.perm is None else self.perm[h0:h1].contiguous(),
-                                      out_peers=self.out_peers(c))
+            with self._span(f"attention[{c}]", main):
+                flash_attn_gather_kv_func(q, k, v, self.gi[:, h0:h1], residual=None if self.residual is None else self.residual[:, h0:h1],
+                                          perm=None if self.perm is None else self.perm[h0:h1].contiguous(),
+                                          out_peers=self.out_peers(c))
 
     def project_out(self) -> torch.Tensor:
-        return torch.matmul(self.buf.out.view(self.Ls, self.H * self.D), self.wo.t())
+        with self._span("out_gemm", torch.cuda.current_stream()):
+            return torch.matmul(self.buf.out.view(self.Ls, self.H * self.D), self.wo.t())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         events = self.project_and_scatter(x)
         self.attend(events)
-        self._order(self.flag_back, self.group_back)       # every rank's rows have arrived before the projection reads them
+        with self._span("order[back]", torch.cuda.current_stream()):
+            self._order(self.flag_back, self.group_back)   # every rank's rows have arrived before the projection reads them
         return self.project_out()
 
     # FLOPs of one layer call over all ranks: the two projections and the attention on the selected tokens
