@@ -104,7 +104,7 @@ def _config(shape, world: int, args, q_bytes_per_gpu: float):
     """The ``config`` object of the JSON line; both arms build it from the same arguments."""
     if world > 1:
         par = f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" + (f"-scatter_{args.scatter}" if args.ulysses == "fused" else "") + \
-              ("-graph" if args.graph and args.ulysses == "fused" else "") + (f"-reserve{args.reserve_sms}" if args.reserve_sms and args.ulysses == "fused" else "")
+              ("-graph" if args.graph and args.ulysses == "fused" else "")
     else:
         par = "single"
     return {"workload": shape.name, "B": 1, "H": shape.heads, "L": shape.seq_len, "D": shape.head_dim, "groups": shape.n_groups,
@@ -415,14 +415,10 @@ def run_ours(args):
         if args.ulysses == "fused":
             # peer-store scatter in front, attention epilogue storing into the owners' sequence shards
             dma_from = {"sm": None, "mixed": 1, "dma": 0}[args.scatter]
-            if args.reserve_sms:
-                dma_from = None            # every chunk by the scatter kernel, chunks after the first on the reserved SMs
-            ul = UlyssesFusedAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks, dma_from_chunk=dma_from,
-                                       reserve_sms=args.reserve_sms)
+            ul = UlyssesFusedAttention(dist.group.WORLD, L, H, D, torch.bfloat16, dev, chunks=args.chunks, dma_from_chunk=dma_from)
 
             def attn(qh, kh, vh, h0, h1, out_peers):
-                flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], residual=residual[:, h0:h1], out_peers=out_peers,
-                                          max_ctas=ul.attention_ctas(h0 // ul.hc))
+                flash_attn_gather_kv_func(qh, kh, vh, gi[:, h0:h1], residual=residual[:, h0:h1], out_peers=out_peers)
             # one attention kernel per head chunk + three scatter kernels per chunk that is not moved by the copy engines
             launches_per_step = ul.chunks + 3 * (ul.chunks if dma_from is None else min(dma_from, ul.chunks))
         else:
@@ -921,8 +917,6 @@ def main():
     ap.add_argument("--scatter", default="mixed", choices=["sm", "mixed", "dma"],
                     help="N > 1, fused: reshard by the scatter kernel, by the copy engines, or (mixed) kernel for the first "
                          "head chunk and copy engines for the chunks that move under an attention kernel")
-    ap.add_argument("--reserve-sms", type=int, default=0,
-                    help="N > 1, fused: SMs the attention kernels leave to the scatter kernel of the next head chunk (0: none)")
     ap.add_argument("--shape", default="auto", choices=["auto", "c2", "c5"],
                     help="attn workload: c2 = L=32,760 H=24 top-k 2048 (default on one GPU); c5 = attention of the Ulysses "
                          "layer, L=98,280 H=40 top-k 4096 in bf16 (default on several GPUs)")

@@ -98,8 +98,6 @@ typedef struct mcs_gather_attn_args {
   int32_t flags;        /* MCS_ATTN_* bits, 0 for the behaviour described above */
   const uint16_t* gi16; /* with gi == NULL: the same indices in packed form, low 16 bits of every entry ... */
   const uint32_t* gi_hi;/* ... and bit 16 as a bit plane, one 32-bit word per 32 consecutive entries (Sk <= 131,072) */
-  int32_t max_ctas;     /* > 0: the persistent kernel uses at most this many CTAs (one per SM), so that a kernel launched
-                           beside it (the exchange of the next head chunk) finds free SMs; 0: all SMs */
 } mcs_gather_attn_args;
 
 /* With perm != NULL: read the query rows through the permutation but keep out and lse in the permuted
@@ -159,13 +157,6 @@ int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* args, void* const* o
  */
 int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
                         int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream);
-
-/*
- * The same reshard with at most max_ctas CTAs (128 threads each): for a head chunk that is exchanged while an attention
- * kernel launched with args->max_ctas < SM count runs on the other SMs.
- */
-int mcs_ulysses_scatter_limited(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
-                                int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, int32_t max_ctas, void* stream);
 
 /*
  * The same reshard, same arguments and result, issued as one strided 2-D device copy per peer on the copy

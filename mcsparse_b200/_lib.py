@@ -31,7 +31,6 @@ EXPORTED_SYMBOLS = (
     "mcs_dense_attn_fwd",
     "mcs_gather_attn_residual_fwd",
     "mcs_ulysses_scatter",
-    "mcs_ulysses_scatter_limited",
     "mcs_ulysses_scatter_dma",
     "mcs_qkv_norm_rope_scatter",
     "mcs_group_mass",
@@ -66,7 +65,7 @@ class GatherAttnArgs(C.Structure):
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32), ("H", C.c_int32), ("D", C.c_int32),
         ("gather_len", C.c_int32), ("group_rows", C.c_int32), ("dtype", C.c_int32),
         ("softmax_scale", C.c_float), ("flags", C.c_int32),
-        ("gi16", C.c_void_p), ("gi_hi", C.c_void_p), ("max_ctas", C.c_int32),
+        ("gi16", C.c_void_p), ("gi_hi", C.c_void_p),
     ]
 
 
@@ -137,9 +136,6 @@ def lib() -> C.CDLL:
     L.mcs_ulysses_scatter.restype = C.c_int
     L.mcs_ulysses_scatter.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int64, C.c_int64, C.c_void_p]
-    L.mcs_ulysses_scatter_limited.restype = C.c_int
-    L.mcs_ulysses_scatter_limited.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_int64,
-                                              C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
     L.mcs_ulysses_scatter_dma.restype = C.c_int
     L.mcs_ulysses_scatter_dma.argtypes = L.mcs_ulysses_scatter.argtypes
     L.mcs_qkv_norm_rope_scatter.restype = C.c_int

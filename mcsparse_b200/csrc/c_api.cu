@@ -108,8 +108,6 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   if (negate && a->residual == nullptr) return MCS_ERR_NULL_POINTER;
   if (a->flags & ~MCS_ATTN_OUT_GROUP_ORDER) return MCS_ERR_UNSUPPORTED;
   p.out_group_order = (a->flags & MCS_ATTN_OUT_GROUP_ORDER) ? 1 : 0;
-  if (a->max_ctas < 0) return MCS_ERR_BAD_SHAPE;
-  p.max_ctas = a->max_ctas;
   p.out_sign = negate ? -1.f : 1.f;
   p.n_out_peers = n_peers; p.out_rows_per_peer = rows_per_peer;
   for (int i = 0; i < n_peers; ++i) p.out_peer[i] = out_peers[i];
@@ -147,8 +145,7 @@ int mcs_gather_attn_fwd_sharded(const mcs_gather_attn_args* a, void* const* out_
 }
 
 static int ulysses_scatter_checked(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
-                                   int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream, bool dma,
-                                   int max_ctas = 0) {
+                                   int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream, bool dma) {
   if (src == nullptr || dst_peers == nullptr) return MCS_ERR_NULL_POINTER;
   if (n_peers < 1 || n_peers > 16 || rank < 0 || rank >= n_peers || rows < 0 || seg_bytes < 16) return MCS_ERR_BAD_SHAPE;
   if (seg_stride_bytes < seg_bytes || src_row_bytes < seg_stride_bytes * (n_peers - 1) + seg_bytes) return MCS_ERR_BAD_SHAPE;
@@ -157,19 +154,13 @@ static int ulysses_scatter_checked(const void* src, void* const* dst_peers, int3
     if (dst_peers[i] == nullptr) return MCS_ERR_NULL_POINTER;
     if (!aligned16(dst_peers[i])) return MCS_ERR_BAD_ALIGNMENT;
   }
-  if (dma) return mcs::launch_ulysses_scatter_dma(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, static_cast<cudaStream_t>(stream));
-  return mcs::launch_ulysses_scatter(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, static_cast<cudaStream_t>(stream), max_ctas);
+  auto* fn = dma ? mcs::launch_ulysses_scatter_dma : mcs::launch_ulysses_scatter;
+  return fn(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int mcs_ulysses_scatter(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
                         int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, void* stream) {
   return ulysses_scatter_checked(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, stream, false);
-}
-
-int mcs_ulysses_scatter_limited(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,
-                                int64_t seg_bytes, int64_t seg_stride_bytes, int64_t src_row_bytes, int32_t max_ctas, void* stream) {
-  if (max_ctas < 1) return MCS_ERR_BAD_SHAPE;
-  return ulysses_scatter_checked(src, dst_peers, n_peers, rank, rows, seg_bytes, seg_stride_bytes, src_row_bytes, stream, false, max_ctas);
 }
 
 int mcs_ulysses_scatter_dma(const void* src, void* const* dst_peers, int32_t n_peers, int32_t rank, int64_t rows,

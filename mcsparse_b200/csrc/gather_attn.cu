@@ -897,9 +897,7 @@ int launch(const GatherAttnParams& p, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return -8;
   const long long items = (long long)p.B * p.H * p.M;
-  int sms = num_sms();
-  if (p.max_ctas > 0 && p.max_ctas < sms) sms = p.max_ctas;   // the caller keeps some SMs for a kernel that runs beside this one
-  const int grid = (int)(items < sms ? items : sms);
+  const int grid = (int)(items < num_sms() ? items : num_sms());
   DenseTileMaps maps{};
   if (kDense) {
     // K/V tiles of the dense mode are consecutive rows: load them with TMA when the layout allows it

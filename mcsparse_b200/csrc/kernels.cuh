@@ -32,7 +32,6 @@ struct GatherAttnParams {
   int n_out_peers;          // 0 = not sharded
   int out_rows_per_peer;
   int out_group_order;      // 1: with perm, output and lse rows stay in permuted (group) order
-  int max_ctas;             // > 0: use at most this many CTAs (SMs), leaving the others to a concurrent kernel
 };
 
 // Tensor maps of K and V for the dense mode (TMA tile loads of 128 contiguous key rows): 4-D maps with the
@@ -143,6 +142,6 @@ int launch_qkv_epilogue(const QkvEpilogueParams& p, void* const* dst, const long
 int launch_ulysses_scatter_dma(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
                                long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);
 int launch_ulysses_scatter(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
-                           long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream, int max_ctas = 0);
+                           long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream);
 
 }  // namespace mcs

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kScatterThreads, 4) ulysses_scatter_kernel(con
 }  // namespace
 
 int launch_ulysses_scatter(const void* src, void* const* dst_peers, int n_peers, int rank, long long rows,
-                           long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream, int max_ctas) {
+                           long long seg_bytes, long long seg_stride_bytes, long long src_row_bytes, cudaStream_t stream) {
   if (n_peers < 1 || n_peers > kMaxPeers) return -2;
   PeerTable tab{};
   for (int i = 0; i < n_peers; ++i) tab.dst[i] = static_cast<uint8_t*>(dst_peers[i]);
@@ -76,7 +76,6 @@ int launch_ulysses_scatter(const void* src, void* const* dst_peers, int n_peers,
   const long long per_block = (long long)kScatterThreads * kUnroll;
   long long blocks = (total + per_block - 1) / per_block;
   if (blocks > 148 * 2) blocks = 148 * 2;
-  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;          // run beside a kernel that left only a few SMs free
   const uint8_t* s8 = static_cast<const uint8_t*>(src);
   if (total + (long long)blocks * per_block < (1ll << 32))
     ulysses_scatter_kernel<uint32_t><<<(unsigned)blocks, kScatterThreads, 0, stream>>>(s8, tab, rank, rows, seg_chunks, row_chunks,

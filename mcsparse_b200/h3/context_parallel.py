@@ -219,19 +219,13 @@ class UlyssesSparseAttention:
 
 
 def ulysses_scatter(src: torch.Tensor, dst_ptrs: Sequence[int], rank: int, rows: int, seg_bytes: int,
-                    seg_stride_bytes: int, src_row_bytes: int, dma: bool = False, max_ctas: int = 0) -> None:
+                    seg_stride_bytes: int, src_row_bytes: int, dma: bool = False) -> None:
     """Launch ``mcs_ulysses_scatter`` on the current stream: segment r of every local row goes to peer r.
     ``dma`` issues the same reshard as strided device copies on the copy engines (``mcs_ulysses_scatter_dma``)."""
     import ctypes as C
     from .. import _lib
     table = (C.c_void_p * len(dst_ptrs))(*[int(x) for x in dst_ptrs])
     stream = torch.cuda.current_stream(src.device).cuda_stream
-    if max_ctas > 0 and not dma:
-        rc = _lib.lib().mcs_ulysses_scatter_limited(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows),
-                                                    int(seg_bytes), int(seg_stride_bytes), int(src_row_bytes), int(max_ctas),
-                                                    C.c_void_p(stream))
-        _lib.raise_on_error(rc, "mcs_ulysses_scatter_limited")
-        return
     fn = _lib.lib().mcs_ulysses_scatter_dma if dma else _lib.lib().mcs_ulysses_scatter
     rc = fn(C.c_void_p(src.data_ptr()), table, len(dst_ptrs), int(rank), int(rows), int(seg_bytes), int(seg_stride_bytes),
             int(src_row_bytes), C.c_void_p(stream))
@@ -296,14 +290,11 @@ class UlyssesFusedAttention:
 
     def __init__(self, group, seq_len: int, heads: int, head_dim: int, dtype, device, chunks: int = 2,
                  buffers: Optional[PeerBuffers] = None, rank: Optional[int] = None, world: Optional[int] = None,
-                 dma_from_chunk: Optional[int] = 1, reserve_sms: int = 0):
+                 dma_from_chunk: Optional[int] = 1):
         # head chunks from this one on are exchanged by the copy engines: they move while the attention of
         # an earlier chunk owns the SMs, where a scatter kernel could not become resident.  Chunk 0 has
         # the GPU to itself and uses the kernel.  None: the kernel for every chunk.
         self.dma_from_chunk = dma_from_chunk
-        # reserve_sms > 0: the attention kernels leave that many SMs free and the scatter kernels of the chunks after the
-        # first are limited to them, so that the exchange of chunk c+1 runs BESIDE the attention of chunk c
-        self.reserve_sms = int(reserve_sms)
         self.group = group
         self.world = world if world is not None else dist.get_world_size(group)
         self.rank = rank if rank is not None else dist.get_rank(group)
@@ -341,20 +332,12 @@ class UlyssesFusedAttention:
         plane = self.L * hc * D * es                       # bytes of one of q / k / v inside recv[c]
         for i, t in enumerate((q, k, v)):
             src = t.view(self.Ls, H, D)[:, c * hc:, :]     # chunk c of rank 0's heads; peers follow at seg_stride
-            ulysses_scatter(src, [p + i * plane for p in self.buf.recv_ptrs[c]], self.rank, self.Ls, seg, seg_stride, row, dma=dma,
-                            max_ctas=4 * self.reserve_sms if (self.reserve_sms and c > 0) else 0)
+            ulysses_scatter(src, [p + i * plane for p in self.buf.recv_ptrs[c]], self.rank, self.Ls, seg, seg_stride, row, dma=dma)
 
     def out_peers(self, c: int):
         """(pointers, rows per peer, strides) for the attention of head chunk c."""
         off = (self.rank * self.Hl + c * self.hc) * self.D * self.esize
         return ([p + off for p in self.buf.out_ptrs], self.Ls, (self.Ls * self.H * self.D, self.H * self.D, self.D))
-
-    def attention_ctas(self, c: int) -> int:
-        """``max_ctas`` for the attention kernel of chunk c: all SMs for the last chunk (nothing is exchanged beside it)."""
-        if not self.reserve_sms or c == self.chunks - 1:
-            return 0
-        sms = torch.cuda.get_device_properties(self.flag.device).multi_processor_count
-        return max(1, sms - self.reserve_sms)
 
     def forward(self, q, k, v, attn_fn):
         """q, k, v: (1, L/N, H, D) sequence shards.  Returns this rank's (1, L/N, H, D) output shard."""

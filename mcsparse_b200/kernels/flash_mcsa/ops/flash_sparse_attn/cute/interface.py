@@ -18,7 +18,6 @@ makes around the kernel into the kernel itself:
               ``out[b, perm[i], h]`` (reference: apply_perm before / invert_perm after,
               token_sparse.py:1057-1060);
 ``group_rows`` query rows per index group (reference tile: 128);
-``max_ctas``  use at most this many SMs (0: all), leaving the rest to a kernel that runs beside this one;
 ``out_group_order`` with ``perm``: only Q is read through the permutation, output and lse rows stay in
               the permuted order (what the anchor step's residual construction works in).
 """
@@ -268,7 +267,6 @@ def flash_attn_gather_kv_func(
     out_peers=None,
     residual_minus_attention: bool = False,
     out_group_order: bool = False,
-    max_ctas: int = 0,
 ):
     """Forward-only token-level sparse gather-KV attention on B200.
 
@@ -344,7 +342,6 @@ def flash_attn_gather_kv_func(
     if out_peers is not None:
         args.out = None
         args.o_stride[0], args.o_stride[1], args.o_stride[2] = (int(x) for x in out_peers[2])
-    args.max_ctas = int(max_ctas)
     if out_group_order and perm is not None:
         if out_peers is not None:
             raise ValueError("out_group_order and out_peers cannot be combined")

@@ -75,36 +75,3 @@ def test_scatter_and_sharded_argument_checks(cuda_device):
     assert L.mcs_ulysses_scatter(src, ok, 2, 0, 4, 250, 256, 512, s) == _lib.MCS_ERR_BAD_ALIGNMENT  # segment not 16-byte
     assert L.mcs_ulysses_scatter(src, ok, 2, 0, 4, 256, 256, 384, s) == _lib.MCS_ERR_BAD_SHAPE      # row too short
     assert L.mcs_ulysses_scatter(src, ok, 17, 0, 4, 256, 256, 8192, s) == _lib.MCS_ERR_BAD_SHAPE    # too many peers
-
-
-def test_reserved_sms_give_the_same_result(cuda_device):
-    """Attention limited to a part of the SMs (``max_ctas``) and the scatter kernel limited to a few CTAs: the
-    arrangement in which the exchange of the next head chunk runs beside the attention kernel.  Same bits."""
-    from mcsparse_b200 import synth
-    from mcsparse_b200.h3.context_parallel import PeerBuffers, UlyssesFusedAttention
-    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
-    dev = cuda_device
-    world, L, H, D, topk = 2, 4096, 4, 128, 256
-    Ls, Hl = L // world, H // world
-    g = torch.Generator().manual_seed(9)
-    q, k, v = (torch.randn(1, L, H, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
-    gi = synth.random_sorted_indices(1, H, L // 128, topk, L, seed=2, device=dev)
-    want, _ = flash_attn_gather_kv_func(q, k, v, gi)
-    bufs = PeerBuffers.emulated(world, L, Ls, H, 1, Hl, D, torch.bfloat16, dev)
-    ranks = [UlyssesFusedAttention(None, L, H, D, torch.bfloat16, dev, chunks=Hl, buffers=bufs[r], rank=r, world=world,
-                                   dma_from_chunk=None, reserve_sms=16) for r in range(world)]
-    shard = lambda t, r: t[:, r * Ls:(r + 1) * Ls].contiguous()
-    for r, u in enumerate(ranks):
-        assert u.attention_ctas(0) == torch.cuda.get_device_properties(dev).multi_processor_count - 16 and u.attention_ctas(u.chunks - 1) == 0
-        for c in range(u.chunks):
-            u.scatter_chunk(shard(q, r), shard(k, r), shard(v, r), c)          # chunk 1 goes through the limited kernel
-    torch.cuda.synchronize()
-    for r, u in enumerate(ranks):
-        for c in range(u.chunks):
-            h0 = r * Hl + c
-            rc = u.buf.recv[c]
-            flash_attn_gather_kv_func(rc[0].unsqueeze(0), rc[1].unsqueeze(0), rc[2].unsqueeze(0), gi[:, h0:h0 + 1],
-                                      out_peers=u.out_peers(c), max_ctas=u.attention_ctas(c) or 7)
-    torch.cuda.synchronize()
-    out = torch.cat([bufs[r].out for r in range(world)], dim=0).unsqueeze(0)
-    assert torch.equal(out, want)
