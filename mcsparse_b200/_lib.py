@@ -11,7 +11,8 @@ import ctypes as C
 import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libmcsparse_b200.so"
+# (MCSPARSE_B200_LIB points at another build of the library, e.g. an experimental variant)
+LIB_PATH = Path(os.environ.get("MCSPARSE_B200_LIB") or Path(__file__).resolve().parent / "libmcsparse_b200.so")
 
 MCS_DTYPE_BF16 = 0
 MCS_DTYPE_FP16 = 1
