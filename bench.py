@@ -508,7 +508,7 @@ def run_ours(args):
     _lib.check_status(dev, "bench timed region")
 
     # ---- end to end through the public entry point with host buffers
-    e2e_steps = max(2, min(args.steps, 5))
+    e2e_steps = max(2, min(args.steps, 10))
     if world == 1:
         # Host tensors in (B, H, L, D) storage (the entry point takes them as strided (B, L, H, D) views), so that
         # a head chunk is one contiguous block.  Three streams: inbound copies of chunk c+1, the kernel on chunk c
@@ -522,17 +522,27 @@ def run_ours(args):
         n_ch = H // hcn
         e2e_launches = n_ch
 
+        prev = {"k": None, "o": None}      # the previous step's per-chunk events: kernel done, outbound copy done
+
         def e2e_step():
+            # Steps follow each other as a stream of requests would: the inbound copy of chunk c of the next step may start
+            # as soon as this step's kernel on chunk c has read its inputs, and a kernel may overwrite its output chunk as
+            # soon as the previous step's outbound copy of that chunk is done.  Every step still moves all of its inputs
+            # in and all of its output out.
             main = torch.cuda.current_stream()
-            start = torch.cuda.Event()
-            start.record(main)
-            s_in.wait_event(start)            # the previous step's kernels have read dq/dk/dv
-            s_out.wait_event(start)
             ev_in = [torch.cuda.Event() for _ in range(n_ch)]
             ev_k = [torch.cuda.Event() for _ in range(n_ch)]
+            ev_o = [torch.cuda.Event() for _ in range(n_ch)]
+            if prev["k"] is None:
+                start = torch.cuda.Event()
+                start.record(main)
+                s_in.wait_event(start)
+                s_out.wait_event(start)
             with torch.cuda.stream(s_in):
                 for c in range(n_ch):
                     sl = slice(c * hcn, (c + 1) * hcn)
+                    if prev["k"] is not None:
+                        s_in.wait_event(prev["k"][c])
                     dq[:, sl].copy_(hq[:, sl], non_blocking=True)
                     dk[:, sl].copy_(hk[:, sl], non_blocking=True)
                     dv[:, sl].copy_(hv[:, sl], non_blocking=True)
@@ -540,24 +550,34 @@ def run_ours(args):
             for c in range(n_ch):
                 sl = slice(c * hcn, (c + 1) * hcn)
                 main.wait_event(ev_in[c])
+                if prev["o"] is not None:
+                    main.wait_event(prev["o"][c])
                 flash_attn_gather_kv_func(dq[:, sl].transpose(1, 2), dk[:, sl].transpose(1, 2), dv[:, sl].transpose(1, 2),
                                           gi[:, sl], out=do[:, sl].transpose(1, 2), residual=residual[:, sl])
                 ev_k[c].record(main)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_k[c])
                     hout[:, sl].copy_(do[:, sl], non_blocking=True)
-            done = torch.cuda.Event()
-            done.record(s_out)
-            main.wait_event(done)
+                    ev_o[c].record(s_out)
+            prev["k"], prev["o"] = ev_k, ev_o
+
+        def e2e_drain():
+            # the timed region ends when the last outbound copy has landed
+            if prev["o"] is not None:
+                torch.cuda.current_stream().wait_event(prev["o"][-1])
         h2d = 3 * q.numel() * q.element_size()
         d2h = out.numel() * out.element_size()
-        e2e_desc = f"pinned host q,k,v in / out, {n_ch} head chunks of {hcn}, inbound copies, kernel and outbound copy on three streams"
+        e2e_desc = (f"pinned host q,k,v in / out, {n_ch} head chunks of {hcn}; inbound copies, kernels and outbound copies on three "
+                    "streams, consecutive steps overlap chunk by chunk")
     else:
         # host sequence shard -> device -> scatter to the peers -> attention -> rows stored into the owners' shards
         # -> host: the exchange in both directions is inside the step
         hq, hk, hv = (t.cpu().pin_memory() for t in (q_s, k_s, v_s))
         hout = torch.empty(1, Ls, H, D, dtype=torch.bfloat16).pin_memory()
         e2e_launches = launches_per_step
+
+        def e2e_drain():
+            pass
 
         def e2e_step():
             q_s.copy_(hq, non_blocking=True)
@@ -570,11 +590,13 @@ def run_ours(args):
         e2e_desc = "pinned host sequence shards in, Ulysses step (exchange both ways inside), output shard to pinned host"
 
     e2e_step()
+    e2e_drain()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_drain()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
@@ -925,7 +947,7 @@ def main():
     ap.add_argument("--layer", action="store_true", help="one GPU with --shape c5: also time the whole Ulysses layer")
     ap.add_argument("--no-layer", action="store_true", help="N > 1: skip the measurement of the whole layer")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
-    ap.add_argument("--e2e-chunk", type=int, default=2, help="heads per chunk of the pipelined end-to-end step (one GPU)")
+    ap.add_argument("--e2e-chunk", type=int, default=8, help="heads per chunk of the pipelined end-to-end step (one GPU)")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8", "layer"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
                          "attn_fp8: the e4m3 variant at the long-video shape (1 GPU); layer: the whole Ulysses DiT attention layer (1 GPU)")
