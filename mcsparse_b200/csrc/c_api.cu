@@ -121,8 +121,12 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
     return mcs::launch_gather_attn_e4m3(p, s);
   }
   if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;
-  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  if (a->D != 64 && a->D != 128) {
+    // other head dimensions (96, 144, 160, 192, 256 ...): the kernel that pads rows on their way into shared memory
+    if (a->D < 8 || a->D > 256 || a->D % 8 != 0) return MCS_ERR_BAD_HEAD_DIM;
+    return mcs::launch_gather_attn_wide(p, a->dtype == MCS_DTYPE_FP16, s);
+  }
   return mcs::launch_gather_attn_16bit(p, a->dtype == MCS_DTYPE_FP16, s);
 }
 

@@ -299,8 +299,10 @@ def flash_attn_gather_kv_func(
 
     alignment = 16 // q.element_size()
     _validate_head_dims(head_dim, head_dim_v, alignment)
-    if head_dim_v != head_dim or head_dim not in (64, 128):
-        raise ValueError(f"Unsupported head_dim={head_dim}/head_dim_v={head_dim_v}: this build supports 64 and 128")
+    # 64 and 128 run on the persistent kernel; every other multiple of 8 up to 256 (the reference lists 96, 144 padded
+    # to 160, 192 and 256, interface.py:45-74) on the kernel that pads rows on their way into shared memory
+    if head_dim_v != head_dim:
+        raise ValueError(f"Unsupported head_dim={head_dim}/head_dim_v={head_dim_v}: head_dim_v must equal head_dim")
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(head_dim)
     if tile_mn is not None and tuple(tile_mn) != (128, _TILE_N):
