@@ -100,7 +100,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def _config(shape, world: int, args, q_bytes_per_gpu: float):
+def _config(shape, world: int, args, q_bytes_per_gpu: float, indices: str = ""):
     """The ``config`` object of the JSON line; both arms build it from the same arguments."""
     if world > 1:
         par = f"ulysses{world}-{args.ulysses}-chunks{args.chunks}" + (f"-scatter_{args.scatter}" if args.ulysses == "fused" else "") + \
@@ -109,7 +109,7 @@ def _config(shape, world: int, args, q_bytes_per_gpu: float):
         par = "single"
     return {"workload": shape.name, "B": 1, "H": shape.heads, "L": shape.seq_len, "D": shape.head_dim, "groups": shape.n_groups,
             "topk": shape.topk, "residual": "fused",
-            "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass, ascending", "parallelism": par,
+            "indices": indices or f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass, ascending", "parallelism": par,
             "l2": f"inputs ({q_bytes_per_gpu / 1e9:.2f} GB per call and GPU) larger than L2; no explicit flush"}
 
 
@@ -394,6 +394,14 @@ def run_ours(args):
         # reduced head count: a small case of the same kernel for profiler captures, not a bench line
         import dataclasses
         shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
+    wide = bool(args.head_dim) and args.head_dim not in (64, 128)
+    if args.head_dim:
+        # another head dimension on the same grid: not a bench line of the headline metric; the sizes other than 64 and
+        # 128 run on the kernel that pads rows on their way into shared memory
+        import dataclasses
+        if world > 1:
+            raise RuntimeError("--head-dim is a one-GPU option")
+        shape = dataclasses.replace(shape, head_dim=args.head_dim, name=shape.name + f"_D{args.head_dim}")
     H, L, D = shape.heads, shape.seq_len, shape.head_dim
     if H % world or L % world:
         raise RuntimeError(f"heads ({H}) and sequence ({L}) must divide by the number of ranks ({world})")
@@ -403,7 +411,11 @@ def run_ours(args):
     residual = synth.residual_like(shape, heads=Hl, head_offset=rank * Hl, device=dev)
     # indices as the configuration defines them: 4 sinks + top-(topk-4) tokens by exact fp32 group mass,
     # built once with this package's own anchor-step kernels (group mass + top-k), outside the timed region
-    gi = synth.topmass_indices(q, k, shape)
+    if wide:
+        # (the group-mass kernel exists for head dimensions 64 and 128 only)
+        gi = synth.random_sorted_indices(1, Hl, shape.n_groups, shape.topk, L, seed=3, device=dev)
+    else:
+        gi = synth.topmass_indices(q, k, shape)
     torch.cuda.synchronize()
     out = torch.empty_like(q)
 
@@ -632,17 +644,18 @@ def run_ours(args):
                     "frac": achieved / peaks["bf16_tflops"],
                     # DRAM bytes per launch from an ncu capture of a 4-head launch of this kernel and workload
                     # (dram__bytes_read.sum + dram__bytes_write.sum), scaled by heads: traffic grows with the heads
-                    "traffic": NCU_DRAM_BYTES_PER_HEAD.get(which, 0) * Hl or None,
+                    "traffic": (0 if args.head_dim else NCU_DRAM_BYTES_PER_HEAD.get(which, 0)) * Hl or None,
                     "traffic_source": "ncu, 4-head capture scaled by heads (profiles/)",
                     "algorithmic_bytes_per_launch": 5 * q.numel() * 2 + gi.numel() * 4,
                     "peak_source": peaks["source"] + " cuBLAS bf16 burst",
-                    "kernel": "gather_attn_kernel<128,bf16>",
+                    "kernel": f"gather_attn_wide_kernel<{(D + 63) // 64},bf16>" if wide else f"gather_attn_kernel<{D},bf16>",
                     "algorithmic_flops_per_launch": shape.attn_flops(Hl)}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": _config(shape, world, args, _input_bytes_per_gpu(shape, world)),
+            "config": _config(shape, world, args, _input_bytes_per_gpu(shape, world),
+                              indices=f"4 sinks + {shape.topk - 4} random tokens, ascending" if wide else ""),
             "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps, "gpu_launches_per_step": e2e_launches, "how": e2e_desc},
@@ -947,6 +960,9 @@ def main():
     ap.add_argument("--layer", action="store_true", help="one GPU with --shape c5: also time the whole Ulysses layer")
     ap.add_argument("--no-layer", action="store_true", help="N > 1: skip the measurement of the whole layer")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the result with the CPU oracle / the single-GPU run")
+    ap.add_argument("--head-dim", type=int, default=0,
+                    help="one GPU: the same grid with another head dimension (a multiple of 8 up to 256); random sorted indices "
+                         "when it is not 64 or 128")
     ap.add_argument("--e2e-chunk", type=int, default=8, help="heads per chunk of the pipelined end-to-end step (one GPU)")
     ap.add_argument("--workload", default="attn", choices=["attn", "anchor", "attn_fp8", "layer"],
                     help="attn: the headline reuse-step attention; anchor: times the anchor-step kernels (1 GPU); "
