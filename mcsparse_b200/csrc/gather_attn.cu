@@ -826,10 +826,14 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
         if (t == 0 && ic > 0 && !mbar_wait(bar(BAR_O_EMPTY), (ic - 1) & 1, p.status, 32)) { ok = false; break; }
         const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
         fence_proxy_async_smem();
+        // Both halves of P before the first product: each product adds to ALL columns of O, and when the running
+        // maximum was raised each of the row's two threads rescales its own half of them first; a product issued on
+        // one stream's arrival alone could land in columns the other thread is still rescaling.
+        if (!wait_if(pa_ready, bar(BAR_P_READY + buf), (g >> 1) & 1, 33) ||
+            !wait_if(pb_ready, bar(BAR_P_READY + 2 + buf), (g >> 1) & 1, 33)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (!wait_if(x == 0 ? pa_ready : pb_ready, bar(BAR_P_READY + 2 * x + buf), (g >> 1) & 1, 33)) { ok = false; break; }
-          tc_fence_after();
           const uint32_t tP = tmem + kColP + buf * 64 + x * 32;
           const uint32_t tO = tmem + kColO;
           if constexpr (kFp8) {

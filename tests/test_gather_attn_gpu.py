@@ -138,6 +138,32 @@ def test_large_logits_rescale_path(cuda_device):
     assert (lse - ref_lse).abs().max() < 2e-2
 
 
+def test_late_maxima_repeated_launches_bit_identical(cuda_device):
+    """Many rows whose running maximum is raised several times (every raise rescales the output accumulator, half
+    of the columns by each of the row's two softmax threads, between two P V products): results within tolerance
+    and the same bits on every launch."""
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_func
+    H, Sq, Sk, D = 4, 2048, 4096, 128
+    g = torch.Generator().manual_seed(21)
+    cent = 1.5 * torch.randn(16, D, generator=g)
+    cid_q = torch.randint(0, 16, (Sq,), generator=g)
+    cid_k = torch.arange(Sk) * 16 // Sk              # keys in cluster order: each row meets its own cluster late
+    q = (cent[cid_q].unsqueeze(1) + 0.3 * torch.randn(Sq, H, D, generator=g)).unsqueeze(0).to(torch.bfloat16)
+    k = (cent[cid_k].unsqueeze(1) + 0.3 * torch.randn(Sk, H, D, generator=g)).unsqueeze(0).to(torch.bfloat16)
+    v = torch.randn(1, Sk, H, D, generator=g).to(torch.bfloat16)
+    gi = torch.arange(0, Sk, 2, dtype=torch.int32).view(1, 1, 1, Sk // 2).expand(1, H, Sq // 128, Sk // 2).contiguous()
+    dev = cuda_device
+    qd, kd, vd, gd = q.to(dev), k.to(dev), v.to(dev), gi.to(dev)
+    out, _ = flash_attn_gather_kv_func(qd, kd, vd, gd)
+    torch.cuda.synchronize()
+    ref, _ = gather_attn_ref(q, k, v, gi)
+    mx, mr = error_metrics(out.float().cpu(), ref)
+    assert mx < BF16_MAX_ABS and mr < BF16_MEAN_REL, (mx, mr)
+    for _ in range(10):
+        again, _ = flash_attn_gather_kv_func(qd, kd, vd, gd)
+        assert torch.equal(again, out)
+
+
 def test_argument_errors(cuda_device):
     from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_func, flash_attn_gather_kv_func
     dev = cuda_device

@@ -146,6 +146,12 @@ def test_c3_fp8_one_head(cuda_device):
     mx, mr = error_metrics(out.float().cpu(), ref)
     assert mx < FP8_MAX_ABS and mr < FP8_MEAN_REL, (mx, mr)
     assert float((lse.cpu() - ref_lse).abs().max()) < 5e-2
+    # The result does not depend on timing: repeated launches give the same bits.  (The e4m3 path raises the running
+    # maximum often; a P V product issued on one column stream's arrival alone could once land in output columns the
+    # row's other thread was still rescaling - rare, and visible only as a handful of rows off by 0.06-0.25.)
+    for _ in range(12):
+        again, _ = flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, scale_qk, sv.float(), return_lse=True, residual=res)
+        assert torch.equal(again, out)
 
 
 @pytest.mark.parametrize("world", [8])
