@@ -587,19 +587,48 @@ def run_ours(args):
         hq, hk, hv = (t.cpu().pin_memory() for t in (q_s, k_s, v_s))
         hout = torch.empty(1, Ls, H, D, dtype=torch.bfloat16).pin_memory()
         e2e_launches = launches_per_step
-
-        def e2e_drain():
-            pass
+        # Two sets of device input shards and two copy streams: the inbound copy of step i+1 runs while step i computes
+        # and while the output shard of step i-1 goes back (the two directions of the host link run at once); every
+        # step still moves all of its inputs in and its output out.
+        sets = [(q_s, k_s, v_s), tuple(torch.empty_like(t) for t in (q_s, k_s, v_s))]
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        st = {"i": 0, "computed": [None, None], "out_done": None}
 
         def e2e_step():
-            q_s.copy_(hq, non_blocking=True)
-            k_s.copy_(hk, non_blocking=True)
-            v_s.copy_(hv, non_blocking=True)
-            o = eager_step()
-            hout.copy_(o, non_blocking=True)
+            main = torch.cuda.current_stream()
+            i = st["i"]
+            cur = sets[i & 1]
+            ev_in = torch.cuda.Event()
+            with torch.cuda.stream(s_in):
+                if st["computed"][i & 1] is not None:
+                    s_in.wait_event(st["computed"][i & 1])     # the step that last read this set has finished
+                else:
+                    s_in.wait_stream(main)
+                for d, h in zip(cur, (hq, hk, hv)):
+                    d.copy_(h, non_blocking=True)
+                ev_in.record(s_in)
+            main.wait_event(ev_in)
+            if st["out_done"] is not None:
+                main.wait_event(st["out_done"])                # the output shard is overwritten by this step
+            o = ul.forward(*cur, attn)
+            ev_c = torch.cuda.Event()
+            ev_c.record(main)
+            st["computed"][i & 1] = ev_c
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c)
+                hout.copy_(o, non_blocking=True)
+                ev_o = torch.cuda.Event()
+                ev_o.record(s_out)
+            st["out_done"] = ev_o
+            st["i"] = i + 1
+
+        def e2e_drain():
+            if st["out_done"] is not None:
+                torch.cuda.current_stream().wait_event(st["out_done"])
         h2d = 3 * q_s.numel() * q_s.element_size()
         d2h = hout.numel() * hout.element_size()
-        e2e_desc = "pinned host sequence shards in, Ulysses step (exchange both ways inside), output shard to pinned host"
+        e2e_desc = ("pinned host sequence shards in, Ulysses step (exchange both ways inside), output shard to pinned host; inbound "
+                    "copy of the next step and outbound copy of the previous one overlap the step")
 
     e2e_step()
     e2e_drain()
@@ -625,7 +654,7 @@ def run_ours(args):
     if (world > 1 or args.layer) and not args.no_layer and which == "c5" and not args.heads:
         # free what the attention-core measurement held, then measure the whole layer
         if world > 1:
-            del ul, q_s, k_s, v_s
+            del ul, q_s, k_s, v_s, sets
         del hq, hk, hv, hout
         torch.cuda.empty_cache()
         layer_rec = _layer_bench(args, shape, world, rank, dev, steps=max(3, min(args.steps, 10)))
