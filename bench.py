@@ -519,6 +519,22 @@ def run_ours(args):
     _lib.lib().mcs_set_clock_buffer(None)
     _lib.check_status(dev, "bench timed region")
 
+    # ---- the floor under the kernel that is not the tensor pipe: the launch's K/V row gather alone (same grid, item walk
+    # and copy routine as the attention kernel's producer warps, nothing else running), timed the same way
+    gather_ms = None
+    if world == 1 and not wide:
+        from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import gather_rate_probe
+        for _ in range(3):
+            gather_rate_probe(q, k, v, gi)
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            gather_rate_probe(q, k, v, gi)
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = g0.elapsed_time(g1) / 5
+
     # ---- end to end through the public entry point with host buffers
     e2e_steps = max(2, min(args.steps, 10))
     if world == 1:
@@ -679,6 +695,13 @@ def run_ours(args):
                     "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                     "kernel": f"gather_attn_wide_kernel<{(D + 63) // 64},bf16>" if wide else f"gather_attn_kernel<{D},bf16>",
                     "algorithmic_flops_per_launch": shape.attn_flops(Hl)}
+        if gather_ms is not None and kern_ms:
+            gbytes = 2.0 * gi.numel() * D * q.element_size()       # every selected K row and V row once per query group
+            roofline["l2_gather"] = {
+                "what": "second bound of the same kernel: every query group pulls its selected K/V rows out of L2 into shared "
+                        "memory; gather_only = the launch's row gather alone (mcs_gather_rate_probe), same grid and copy routine",
+                "bytes_per_launch": gbytes, "gather_only_ms": gather_ms, "gather_only_gbs": gbytes / gather_ms / 1e6,
+                "in_kernel_gbs": gbytes / kern_ms / 1e6, "frac": gather_ms / kern_ms}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,

@@ -345,6 +345,16 @@ int mcs_perm_invert(const void* x, void* out, const int64_t* perm, int32_t BH, i
                     int64_t x_bh_bytes, int64_t x_row_bytes, int64_t o_bh_bytes, int64_t o_row_bytes, void* stream);
 
 /*
+ * Gather-rate probe (no reference counterpart; measurement aid).  Takes the argument block of
+ * mcs_gather_attn_fwd (int32 index list, head dimension 64 or 128) and launches only the K/V row gather of
+ * that call: same grid, same walk over the query groups, same four copying warps per CTA and the same 16-byte
+ * copies into swizzled shared-memory tiles, which nothing reads.  Its duration is the time the selected rows of
+ * one attention launch need to come out of L2 when no other role of the kernel competes - a floor for the
+ * attention launch that its softmax and tensor-core schedule cannot lower.  q, out, residual are not touched.
+ */
+int mcs_gather_rate_probe(const mcs_gather_attn_args* a, void* stream);
+
+/*
  * SM clock probe (no reference counterpart; measurement aid).  Launches one CTA that spins for about
  * 40,000 SM cycles and writes {SM cycles, nanoseconds} it observed to out2[0..1] (device memory, two
  * int64): cycles * 1000 / nanoseconds is the SM clock in MHz at that moment.  Launched right behind a

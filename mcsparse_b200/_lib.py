@@ -49,6 +49,7 @@ EXPORTED_SYMBOLS = (
     "mcs_perm_apply",
     "mcs_perm_invert",
     "mcs_sm_clock_probe",
+    "mcs_gather_rate_probe",
     "mcs_set_clock_buffer",
 )
 
@@ -143,6 +144,8 @@ def lib() -> C.CDLL:
     L.mcs_qkv_norm_rope_scatter.argtypes = [C.POINTER(QkvEpilogueArgs), C.c_void_p]
     L.mcs_set_clock_buffer.restype = None
     L.mcs_set_clock_buffer.argtypes = [C.c_void_p]
+    L.mcs_gather_rate_probe.restype = C.c_int
+    L.mcs_gather_rate_probe.argtypes = [C.POINTER(GatherAttnArgs), C.c_void_p]
     L.mcs_sm_clock_probe.restype = C.c_int
     L.mcs_sm_clock_probe.argtypes = [C.c_void_p, C.c_void_p]
     L.mcs_group_mass.restype = C.c_int

@@ -56,7 +56,7 @@ const char* mcs_error_string(int code) {
 }
 
 static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_peers, int n_peers, int rows_per_peer,
-                                bool dense, void* stream, bool negate = false) {
+                                bool dense, void* stream, bool negate = false, bool probe = false) {
   if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
   if (!dense && a->gi == nullptr && (a->gi16 == nullptr || a->gi_hi == nullptr)) return MCS_ERR_NULL_POINTER;
@@ -114,6 +114,11 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   p.clock_out = g_clock_out;
 
+  if (probe) {
+    // measurement aid: only the K/V row gather of this launch (int32 index list, head dimension 64 or 128)
+    if (a->gi == nullptr || dense) return MCS_ERR_UNSUPPORTED;
+    return mcs::launch_gather_rate_probe(p, esize, s);
+  }
   if (a->dtype == MCS_DTYPE_E4M3) {
     if (a->scale_qk_log2 == nullptr || a->scale_v == nullptr) return MCS_ERR_NULL_POINTER;
     if (a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
@@ -136,6 +141,10 @@ int mcs_gather_attn_fwd(const mcs_gather_attn_args* a, void* stream) {
 
 int mcs_gather_attn_residual_fwd(const mcs_gather_attn_args* a, void* stream) {
   return gather_attn_dispatch(a, nullptr, 0, 0, false, stream, true);
+}
+
+int mcs_gather_rate_probe(const mcs_gather_attn_args* a, void* stream) {
+  return gather_attn_dispatch(a, nullptr, 0, 0, false, stream, false, true);
 }
 
 int mcs_dense_attn_fwd(const mcs_gather_attn_args* a, void* stream) {

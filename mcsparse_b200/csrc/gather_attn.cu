@@ -882,6 +882,48 @@ __global__ void __launch_bounds__(kThreads, 1) gather_attn_kernel(const GatherAt
   }
 }
 
+// Measurement aid: the K/V row gather of a sparse attention launch and nothing else.  Same grid, same item walk,
+// same four producer warps and the same copy routine as the attention kernel; the tiles go into a six-slot ring
+// that nobody reads, four tiles of copies in flight per thread.  Its duration is the time the launch's selected
+// rows need to come out of L2 into shared memory when no other role competes: a floor for the attention kernel
+// that no change to its softmax or tensor-core schedule can lower.
+template <int RB>
+__global__ void __launch_bounds__(kProducerThreads, 1) gather_rate_probe_kernel(const GatherAttnParams p) {
+  constexpr int kTileBytes = (RB / 128) * 16384;
+  constexpr int kSlots = 6;
+  constexpr int kEs = 1;     // RB counts bytes
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int lane = threadIdx.x & 31, pw = threadIdx.x >> 5;
+  const int row0 = pw * kRowsPerProducerWarp, my_row = row0 + lane;
+  const int chunk_off = (lane % (RB / 16)) * 16;
+  const int es = RB / p.D;                      // bytes per element
+  const size_t k_row = (size_t)es * p.k_stride[1], v_row = (size_t)es * p.v_stride[1];
+  const int n_items = p.B * p.H * p.M;
+  int slot = 0;
+  (void)kEs;
+#pragma unroll 1
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const Item it = decode_item(p, item);
+    const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + (size_t)es * ((size_t)it.b * p.k_stride[0] + (size_t)it.h * p.k_stride[2]) + chunk_off;
+    const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v) + (size_t)es * ((size_t)it.b * p.v_stride[0] + (size_t)it.h * p.v_stride[2]) + chunk_off;
+    int idx_next = __ldg(it.gi + my_row);
+#pragma unroll 1
+    for (int t = 0; t < it.T; ++t) {
+      const int idx = min(max(idx_next, 0), p.Sk - 1);
+      if (t + 1 < it.T) idx_next = __ldg(it.gi + (t + 1) * kTileN + my_row);
+      warp_gather_rows<RB>(s_base + slot * kTileBytes, row0, idx, kb, k_row, lane);
+      cp_async_commit_group();
+      slot = slot + 1 == kSlots ? 0 : slot + 1;
+      warp_gather_rows<RB>(s_base + slot * kTileBytes, row0, idx, vb, v_row, lane);
+      cp_async_commit_group();
+      slot = slot + 1 == kSlots ? 0 : slot + 1;
+      cp_async_wait_group<4>();
+    }
+  }
+  cp_async_wait_all();
+}
+
 int num_sms() {
   static int cached[64] = {0};
   int dev = 0;
@@ -924,6 +966,22 @@ int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t 
   if (p.D == 128) return fp16 ? launch<128, 1>(p, stream) : launch<128, 0>(p, stream);
   if (p.D == 64) return fp16 ? launch<64, 1>(p, stream) : launch<64, 0>(p, stream);
   return -3;
+}
+
+int launch_gather_rate_probe(const GatherAttnParams& p, int elem_bytes, cudaStream_t stream) {
+  if (p.gi == nullptr || p.dense || (p.D != 64 && p.D != 128) || (elem_bytes != 1 && elem_bytes != 2)) return -3;
+  const int rb = p.D * elem_bytes;
+  const long long items = (long long)p.B * p.H * p.M;
+  const int grid = (int)(items < num_sms() ? items : num_sms());
+  auto run = [&](auto kern, int tile_bytes) {
+    const int smem = 6 * tile_bytes + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -8;
+    kern<<<grid, kProducerThreads, smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+  };
+  if (rb == 256) return run(gather_rate_probe_kernel<256>, 32768);
+  if (rb == 128) return run(gather_rate_probe_kernel<128>, 16384);
+  return -3;          // 64-byte rows (8-bit, D = 64) are not a configuration of the attention kernel
 }
 
 int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream) {

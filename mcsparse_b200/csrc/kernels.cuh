@@ -118,6 +118,8 @@ int launch_topk_select(const TopkParams& p, cudaStream_t stream);
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_16bit(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
+// measurement aid: the K/V row gather of a sparse launch alone (gather_attn.cu)
+int launch_gather_rate_probe(const GatherAttnParams& p, int elem_bytes, cudaStream_t stream);
 // head dimensions other than 64 and 128 (multiples of 8 up to 256), bf16 / fp16 (gather_attn_wide.cu)
 int launch_gather_attn_wide(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
 

@@ -248,6 +248,28 @@ def _fill_args(q, k, v, out, lse, gi, gl, residual, perm, gather_len, group_rows
     return a
 
 
+def gather_rate_probe(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gather_kv_indices: torch.Tensor,
+                      group_rows: int = 128) -> None:
+    """Measurement aid: launch only the K/V row gather of the sparse attention call with these arguments (same
+    grid, item walk and copy routine as the attention kernel's producer warps; the tiles land in shared memory
+    that nothing reads).  Timed with CUDA events it gives the floor that the L2-to-shared-memory gather puts under
+    the attention launch.  bf16 / fp16 / e4m3 inputs, head dimension 64 or 128 (e4m3: 128), int32 indices."""
+    if not all(t.is_cuda for t in (q, k, v, gather_kv_indices)) or gather_kv_indices.dtype != torch.int32:
+        raise ValueError("gather_rate_probe needs CUDA tensors and an int32 index list")
+    if q.dtype == torch.bfloat16:
+        code = _lib.MCS_DTYPE_BF16
+    elif q.dtype == torch.float16:
+        code = _lib.MCS_DTYPE_FP16
+    elif q.dtype == torch.float8_e4m3fn:
+        code = _lib.MCS_DTYPE_E4M3
+    else:
+        raise TypeError(f"unsupported dtype {q.dtype}")
+    gi = gather_kv_indices.contiguous()
+    args = _fill_args(q, k, v, q, None, gi, None, None, None, gi.shape[-1], int(group_rows), code, 1.0)
+    rc = _lib.lib().mcs_gather_rate_probe(args, torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.raise_on_error(rc, "mcs_gather_rate_probe")
+
+
 def flash_attn_gather_kv_func(
     q: torch.Tensor,
     k: torch.Tensor,

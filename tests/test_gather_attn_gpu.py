@@ -164,6 +164,22 @@ def test_late_maxima_repeated_launches_bit_identical(cuda_device):
         assert torch.equal(again, out)
 
 
+def test_gather_rate_probe_launches(cuda_device):
+    """The measurement aid (only the K/V row gather of a launch) accepts the attention call's arguments, touches no
+    output and leaves the status word clear."""
+    from mcsparse_b200 import _lib
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute.interface import gather_rate_probe
+    dev = cuda_device
+    q, k, v, gi = (t.to(dev) for t in _make(1, 3, 1000, 2000, 128, 512, 128, torch.bfloat16, seed=12))
+    q0 = q.clone()
+    gather_rate_probe(q, k, v, gi)
+    torch.cuda.synchronize()
+    _lib.check_status(dev, "gather_rate_probe")
+    assert torch.equal(q, q0)
+    with pytest.raises(ValueError):
+        gather_rate_probe(q, k, v, gi.long())
+
+
 def test_argument_errors(cuda_device):
     from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_func, flash_attn_gather_kv_func
     dev = cuda_device
