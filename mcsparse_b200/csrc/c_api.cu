@@ -121,8 +121,12 @@ static int gather_attn_dispatch(const mcs_gather_attn_args* a, void* const* out_
   }
   if (a->dtype == MCS_DTYPE_E4M3) {
     if (a->scale_qk_log2 == nullptr || a->scale_v == nullptr) return MCS_ERR_NULL_POINTER;
-    if (a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
     if (a->group_rows != 128) return MCS_ERR_BAD_SHAPE;
+    if (a->D != 128) {
+      // other head dimensions (the reference's FP8 kernel lists 160): the kernel that pads rows into shared memory
+      if (a->D < 16 || a->D > 256 || a->D % 16 != 0) return MCS_ERR_BAD_HEAD_DIM;
+      return mcs::launch_gather_attn_wide_e4m3(p, s);
+    }
     return mcs::launch_gather_attn_e4m3(p, s);
   }
   if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;

@@ -1,10 +1,11 @@
 // Gather-KV sparse flash-attention forward for the head dimensions the main kernel has no instantiation for:
-// any multiple of 8 up to 256 other than 64 and 128 (96, 144, 160, 192, 256 ...), bf16 / fp16.
+// any multiple of 8 up to 256 other than 64 and 128 (96, 144, 160, 192, 256 ...) for bf16 / fp16, and any multiple
+// of 16 up to 256 other than 128 for e4m3 (the reference's FP8 kernel lists 128 and 160).
 //
 // The reference pads 144 to 160 in its wrapper and keeps one compiled kernel per padded size
 // (mcsparse/kernels/flash_mcsa/ops/flash_sparse_attn/cute/interface.py:45-74, :138-159).  Here the padding happens
-// on the way into shared memory: a row is copied in 16-byte chunks into NB = ceil(D / 64) swizzled column blocks
-// and the chunks beyond D are zero-filled, so no padded copy of Q, K or V exists in global memory.
+// on the way into shared memory: a row is copied in 16-byte chunks into NB = ceil(row bytes / 128) swizzled column
+// blocks and the chunks beyond the row are zero-filled, so no padded copy of Q, K or V exists in global memory.
 //
 // Same math and the same argument block as the main kernel (gather_attn.cu); a simpler schedule, because these
 // sizes leave less room: with D = 256 a K or V tile is 64 KB and the output accumulator takes 256 of the 512
@@ -79,8 +80,13 @@ __device__ __forceinline__ void warp_gather_rows_w(uint32_t s_tile, int row0, in
   }
 }
 
-template <int NB, bool kFp16>
+// kType: 0 = bf16, 1 = fp16, 2 = e4m3 (Q/K/V 8-bit, logits scaled by scale_qk_log2[b,h,m], P quantised to e4m3 with a
+// bias of 2^4, O scaled by scale_v[b,h], bf16 out: the contract of the main kernel's e4m3 instantiation)
+template <int NB, int kType>
 __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const GatherAttnParams p) {
+  constexpr bool kFp16 = kType == 1;
+  constexpr bool kFp8 = kType == 2;
+  constexpr int kEs = kFp8 ? 1 : 2;                   // bytes per Q/K/V element
   using L = SmemW<NB>;
   constexpr int R = L::kRing;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -102,9 +108,10 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
   const int rows_valid = min(p.group_rows, p.Sq - row_base);
   int T = p.gather_len / kTileN;
   if (p.gl != nullptr) T = min(max(p.gl[item], 1), T);
-  const int d_chunks = p.D / 8;                   // 16-byte chunks of a row
-  const int ksteps = (p.D + 15) / 16;             // k-steps of Q K^T
-  const int n_pv = ksteps * 16;                   // output columns the P V product computes
+  const int d_chunks = p.D * kEs / 16;            // 16-byte chunks of a Q/K/V row
+  const int ksteps = (p.D * kEs + 31) / 32;       // k-steps of Q K^T (32 bytes of every row each)
+  const int n_pv = (p.D + 15) / 16 * 16;          // output columns the P V product computes
+  const int o_chunks = p.D / 8;                   // 16-byte chunks of an output row (16-bit elements)
 
   if (tid == 0) {
     for (int i = 0; i < R; ++i) {
@@ -119,8 +126,8 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
     mbar_init(bar(WB_DRAIN), 1);
     mbar_fence_init();
   }
-  // S 128 + P 64 + O: heads of up to 64 leave room for two CTAs per SM, each with half of tensor memory
-  constexpr uint32_t kTmemColsW = NB == 1 ? 256 : 512;
+  // S 128 + P 64 + O: 16-bit heads of up to 64 leave room for two CTAs per SM, each with half of tensor memory
+  constexpr uint32_t kTmemColsW = (NB == 1 && !kFp8) ? 256 : 512;
   if (warp == kMmaWarpW) {
     tmem_alloc(smem_u32(tmem_slot), kTmemColsW);
     tmem_relinquish();
@@ -138,8 +145,11 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
     };
     const int r_in = warp * 32 + lane;
     const uint32_t lane_addr = (static_cast<uint32_t>(warp) * 32u) << 16;
-    const float scale_log2 = p.scale_log2;
-    constexpr float kRescale = kFp16 ? 12.0f : 24.0f;     // lazy raise of the running maximum, as in the main kernel
+    const float scale_log2 = kFp8 ? p.scale_qk_log2[item] : p.scale_log2;
+    // lazy raise of the running maximum with the thresholds of the main kernel; e4m3 P is biased by 2^4 so that the
+    // largest probability of a row lies in [2^4, 2^8]
+    constexpr float kRescale = kFp8 ? 4.0f : (kFp16 ? 12.0f : 24.0f);
+    constexpr float kBias = kFp8 ? 4.0f : 0.0f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
 #pragma unroll 1
@@ -170,10 +180,15 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
         }
       }
       const float m_loc = fmaxf(fmax3(mx0, mx1, mx2), mx3) * scale_log2;
-      const bool raise = (m_loc - m_run) > kRescale;
+      bool raise = (m_loc - m_run) > kRescale;
+      if constexpr (kFp8) {
+        // a new maximum that would hold more than an eighth of the mass so far becomes the reference point at once:
+        // its e4m3 probability is then exact (see the main kernel)
+        raise = raise || ((m_loc > m_run) && (ex2_approx(m_loc - m_run + kBias) > 0.125f * l_run));
+      }
       const float alpha = raise ? ex2_approx(m_run - m_loc) : 1.f;
       if (raise) m_run = m_loc;
-      const float neg_m = -m_run;
+      const float neg_m = kBias - m_run;
       // exponentials and packing first (registers only), then the wait for the previous P V
       uint32_t pk[64];
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
@@ -184,8 +199,12 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
         const float p2 = ex2_approx(fmaf(__uint_as_float(sc[i + 2]), scale_log2, neg_m));
         const float p3 = ex2_approx(fmaf(__uint_as_float(sc[i + 3]), scale_log2, neg_m));
         ls0 += p0; ls1 += p1; ls2 += p2; ls3 += p3;
-        pk[i / 2] = kFp16 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
-        pk[i / 2 + 1] = kFp16 ? pack_f16x2(p2, p3) : pack_bf16x2(p2, p3);
+        if constexpr (kFp8) {
+          pk[i / 4] = pack_e4m3x4(p0, p1, p2, p3);
+        } else {
+          pk[i / 2] = kFp16 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+          pk[i / 2 + 1] = kFp16 ? pack_f16x2(p2, p3) : pack_bf16x2(p2, p3);
+        }
       }
       l_run = l_run * alpha + ((ls0 + ls1) + (ls2 + ls3));
       if (g > 0) {
@@ -208,7 +227,7 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
       }
       const uint32_t tP = tmem + kColPW + lane_addr;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) tmem_st8(tP + c * 8, *reinterpret_cast<uint32_t(*)[8]>(&pk[c * 8]));
+      for (int c = 0; c < (kFp8 ? 4 : 8); ++c) tmem_st8(tP + c * 8, *reinterpret_cast<uint32_t(*)[8]>(&pk[c * 8]));
       tmem_wait_st();
       tc_fence_before();
       warp_arrive(bar(WB_P_READY));
@@ -231,10 +250,10 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
       uint8_t* optr = obase + 2 * ((size_t)b * p.o_stride[0] + (size_t)lrow * p.o_stride[1] + (size_t)h * p.o_stride[2]);
       const uint8_t* rptr = p.residual == nullptr ? nullptr
           : reinterpret_cast<const uint8_t*>(p.residual) + 2 * ((size_t)b * p.r_stride[0] + (size_t)h * p.r_stride[1] + (size_t)row * p.r_stride[2]);
-      const float w = p.out_sign / l_run;
+      const float w = p.out_sign * (kFp8 ? p.scale_v[bh] : 1.f) / l_run;
       const uint32_t tO = tmem + kColOW + lane_addr;
 #pragma unroll 1
-      for (int c = 0; c < d_chunks; ++c) {
+      for (int c = 0; c < o_chunks; ++c) {
         uint32_t ra[8];
         tmem_ld8(tO + c * 8, ra);
         tmem_wait_ld();
@@ -246,7 +265,7 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float rx, ry;
-            if (kFp16) {
+            if constexpr (kFp16) {
               const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rw[j]));
               rx = f.x; ry = f.y;
             } else {
@@ -259,7 +278,7 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
           *reinterpret_cast<uint4*>(optr + c * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
       }
-      if (valid && p.lse != nullptr) p.lse[(size_t)bh * p.Sq + orow] = (m_run + lg2_approx(l_run)) * 0.6931471805599453f;
+      if (valid && p.lse != nullptr) p.lse[(size_t)bh * p.Sq + orow] = (m_run + lg2_approx(l_run) - kBias) * 0.6931471805599453f;
     }
     tc_fence_before();
   } else if (warp < kMmaWarpW) {
@@ -267,10 +286,10 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
     const int pw = warp - kProducerWarp0W;
     const int row0 = pw * 32;
     const int my_row = row0 + lane;
-    const size_t q_row = 2 * (size_t)p.q_stride[1], k_row = 2 * (size_t)p.k_stride[1], v_row = 2 * (size_t)p.v_stride[1];
-    const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) + 2 * ((size_t)b * p.q_stride[0] + (size_t)h * p.q_stride[2]);
-    const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + 2 * ((size_t)b * p.k_stride[0] + (size_t)h * p.k_stride[2]);
-    const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v) + 2 * ((size_t)b * p.v_stride[0] + (size_t)h * p.v_stride[2]);
+    const size_t q_row = kEs * (size_t)p.q_stride[1], k_row = kEs * (size_t)p.k_stride[1], v_row = kEs * (size_t)p.v_stride[1];
+    const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) + kEs * ((size_t)b * p.q_stride[0] + (size_t)h * p.q_stride[2]);
+    const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k) + kEs * ((size_t)b * p.k_stride[0] + (size_t)h * p.k_stride[2]);
+    const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v) + kEs * ((size_t)b * p.v_stride[0] + (size_t)h * p.v_stride[2]);
     {
       int src_row = -1;
       if (my_row < rows_valid) {
@@ -324,7 +343,7 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
     tc_fence_before();
   } else {
     // ===================================================================== issuer of both products
-    constexpr uint32_t kFmt = kFp16 ? 0u : 1u;
+    constexpr uint32_t kFmt = (kFp16 || kFp8) ? 0u : 1u;   // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
     constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
     auto desc = [&](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
     constexpr uint32_t kLboK = (16u >> 4) << 16;
@@ -347,7 +366,10 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
 #pragma unroll 1
       for (int j = 0; j < ksteps; ++j) {
         const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
-        if (leader) mma_f16_ss(tmem + kColSW, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+        if (leader) {
+          if constexpr (kFp8) mma_f8_ss(tmem + kColSW, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+          else mma_f16_ss(tmem + kColSW, desc(qlo + koff), desc(klo + koff), idesc_qk, j > 0);
+        }
       }
       if (leader) {
         tc_commit(bar(WB_EMPTY + slot));
@@ -362,10 +384,18 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
       fence_proxy_async_smem();
       tc_fence_after();
       const uint32_t vlo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLboV;
+      if constexpr (kFp8) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // A: 16 packed probabilities = 8 tensor-memory columns per k-step; B: 16 key rows = 2048 bytes
-        if (leader) mma_f16_ts(tmem + kColOW, tmem + kColPW + j * 8, desc(vlo + j * (2048 >> 4)), idesc_pv, (g > 0) || (j > 0));
+        for (int j = 0; j < 4; ++j) {
+          // A: 32 e4m3 probabilities = 8 tensor-memory columns per k-step; B: 32 key rows = 4096 bytes
+          if (leader) mma_f8_ts(tmem + kColOW, tmem + kColPW + j * 8, desc(vlo + j * (4096 >> 4)), idesc_pv, (g > 0) || (j > 0));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // A: 16 packed probabilities = 8 tensor-memory columns per k-step; B: 16 key rows = 2048 bytes
+          if (leader) mma_f16_ts(tmem + kColOW, tmem + kColPW + j * 8, desc(vlo + j * (2048 >> 4)), idesc_pv, (g > 0) || (j > 0));
+        }
       }
       if (leader) {
         tc_commit(bar(WB_EMPTY + slot));
@@ -395,13 +425,16 @@ __global__ void __launch_bounds__(kThreadsW, 1) gather_attn_wide_kernel(const Ga
   }
 }
 
-template <int NB, bool kFp16>
+template <int NB, int kType>
 int launch_wide(const GatherAttnParams& p, cudaStream_t stream) {
   using L = SmemW<NB>;
-  auto kern = gather_attn_wide_kernel<NB, kFp16>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return -8;
+  auto kern = gather_attn_wide_kernel<NB, kType>;
+  // an 8-bit head of up to 128 fits one 128-byte block but needs all of tensor memory: ask for enough shared memory
+  // that only one such CTA is resident per SM
+  const int smem = (kType == 2 && NB == 1 && L::kDynamic < 120 * 1024) ? 120 * 1024 : L::kDynamic;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -8;
   const long long items = (long long)p.B * p.H * p.M;
-  kern<<<static_cast<unsigned>(items), kThreadsW, L::kDynamic, stream>>>(p);
+  kern<<<static_cast<unsigned>(items), kThreadsW, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
@@ -411,11 +444,16 @@ int launch_gather_attn_wide(const GatherAttnParams& p, bool fp16, cudaStream_t s
   if (p.D < 8 || p.D > 256 || p.D % 8 != 0 || p.group_rows > 128) return -3;
   const int nb = (p.D + 63) / 64;
   switch (nb) {
-    case 1: return fp16 ? launch_wide<1, true>(p, stream) : launch_wide<1, false>(p, stream);
-    case 2: return fp16 ? launch_wide<2, true>(p, stream) : launch_wide<2, false>(p, stream);
-    case 3: return fp16 ? launch_wide<3, true>(p, stream) : launch_wide<3, false>(p, stream);
-    default: return fp16 ? launch_wide<4, true>(p, stream) : launch_wide<4, false>(p, stream);
+    case 1: return fp16 ? launch_wide<1, 1>(p, stream) : launch_wide<1, 0>(p, stream);
+    case 2: return fp16 ? launch_wide<2, 1>(p, stream) : launch_wide<2, 0>(p, stream);
+    case 3: return fp16 ? launch_wide<3, 1>(p, stream) : launch_wide<3, 0>(p, stream);
+    default: return fp16 ? launch_wide<4, 1>(p, stream) : launch_wide<4, 0>(p, stream);
   }
+}
+
+int launch_gather_attn_wide_e4m3(const GatherAttnParams& p, cudaStream_t stream) {
+  if (p.D < 16 || p.D > 256 || p.D % 16 != 0 || p.group_rows > 128) return -3;
+  return p.D <= 128 ? launch_wide<1, 2>(p, stream) : launch_wide<2, 2>(p, stream);
 }
 
 }  // namespace mcs

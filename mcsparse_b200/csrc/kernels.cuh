@@ -122,6 +122,7 @@ int launch_gather_attn_e4m3(const GatherAttnParams& p, cudaStream_t stream);
 int launch_gather_rate_probe(const GatherAttnParams& p, int elem_bytes, cudaStream_t stream);
 // head dimensions other than 64 and 128 (multiples of 8 up to 256), bf16 / fp16 (gather_attn_wide.cu)
 int launch_gather_attn_wide(const GatherAttnParams& p, bool fp16, cudaStream_t stream);
+int launch_gather_attn_wide_e4m3(const GatherAttnParams& p, cudaStream_t stream);   // e4m3, multiples of 16 up to 256
 
 // QKV-projection epilogue: RMSNorm + 3-D rotary embedding + store into the (peer) buffers the attention reads (qkv_epilogue.cu)
 constexpr int kQkvMaxSegments = 128;

@@ -395,7 +395,7 @@ def flash_attn_gather_kv_fp8_func(
 
     Pre-quantised entry point; the caller owns quantisation.
 
-    - q=(B, Sq, H, D), k=(B, Sk, H, D), v=(B, Sk, H, D), all float8_e4m3fn, D = 128.
+    - q=(B, Sq, H, D), k=(B, Sk, H, D), v=(B, Sk, H, D), all float8_e4m3fn, D a multiple of 16 up to 256.
       V is passed as it is: the d-column pre-permutation the reference's Hopper
       kernel needs for its in-smem transpose does not exist here.
     - scale_qk_log2=(B, H, ceil(Sq/128)) fp32 = softmax_scale*log2(e)*s_q*s_k
@@ -409,9 +409,11 @@ def flash_attn_gather_kv_fp8_func(
     if not all(t.is_cuda for t in (q, k, v, gather_kv_indices, scale_qk_log2, scale_v)):
         raise RuntimeError("all inputs must be CUDA tensors")
     batch_size, seqlen_q, seqlen_k, num_head, head_dim, head_dim_v = _shape_checks(q, k, v)
-    if head_dim != 128 or head_dim_v != head_dim:
+    # 128 runs on the persistent kernel; other multiples of 16 up to 256 (the reference lists 160) on the kernel that
+    # pads rows on their way into shared memory
+    if head_dim_v != head_dim or head_dim % 16 != 0 or not (16 <= head_dim <= 256):
         raise ValueError(
-            f"fp8 gather-KV forward supports head_dim 128 with head_dim == head_dim_v, "
+            f"fp8 gather-KV forward supports head_dim == head_dim_v, a multiple of 16 up to 256, "
             f"got D={head_dim}, Dv={head_dim_v}")
     num_m_blocks = math.ceil(seqlen_q / 128)
     gather_kv_indices, gather_kv_lengths, gather_len = _index_checks(

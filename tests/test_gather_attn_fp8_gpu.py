@@ -12,10 +12,9 @@ pytestmark = pytest.mark.gpu
 FP8_MAX_ABS, FP8_MEAN_REL = 6e-2, 3e-2
 
 
-def _case(B, H, Sq, Sk, K, seed, clustered=True):
+def _case(B, H, Sq, Sk, K, seed, clustered=True, D=128):
     from mcsparse_b200.synth import quantize_e4m3_per_head
     g = torch.Generator().manual_seed(seed)
-    D = 128
     if clustered:
         cent = torch.randn(H, 16, D, generator=g)
         cq = torch.randint(0, 16, (Sq,), generator=g)
@@ -73,3 +72,27 @@ def test_fp8_argument_errors(cuda_device):
         flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, sqk[:, :1], sv)
     with pytest.raises(TypeError):
         flash_attn_gather_kv_fp8_func(q8, k8, v8, gi, sqk.double(), sv)
+
+
+@pytest.mark.parametrize("D", [160, 256, 64])
+def test_fp8_other_head_dims(cuda_device, D):
+    """The head dimensions other than 128 (the reference's FP8 kernel lists 160, cute/interface.py:358-373) run on the
+    kernel that pads rows into shared memory; residual, permutation, ragged last group, 5 key tiles per group."""
+    from mcsparse_b200.kernels.flash_mcsa.ops.flash_sparse_attn.cute import flash_attn_gather_kv_fp8_func
+    B, H, Sq, Sk, K = 1, 2, 300, 1500, 640
+    q8, k8, v8, gi, sqk, sv = _case(B, H, Sq, Sk, K, 20 + D, clustered=True, D=D)
+    g = torch.Generator().manual_seed(5)
+    residual = (0.1 * torch.randn(B, H, Sq, D, generator=g)).to(torch.bfloat16)
+    perm = torch.stack([torch.randperm(Sq, generator=g) for _ in range(B * H)])
+    dev = cuda_device
+    out, lse = flash_attn_gather_kv_fp8_func(q8.to(dev), k8.to(dev), v8.to(dev), gi.to(dev), sqk.to(dev), sv.to(dev),
+                                             return_lse=True, residual=residual.to(dev), perm=perm.to(dev))
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, H, D)
+    ref, ref_lse = gather_attn_fp8_ref(q8, k8, v8, gi, sqk, sv, residual=residual, perm=perm)
+    mx, mr = error_metrics(out.float().cpu(), ref)
+    assert mx < FP8_MAX_ABS and mr < FP8_MEAN_REL, (D, mx, mr)
+    assert (lse.cpu() - ref_lse).abs().max() < 5e-2
+    again, _ = flash_attn_gather_kv_fp8_func(q8.to(dev), k8.to(dev), v8.to(dev), gi.to(dev), sqk.to(dev), sv.to(dev),
+                                             residual=residual.to(dev), perm=perm.to(dev))
+    assert torch.equal(again, out)
