@@ -868,6 +868,10 @@ def run_fp8(args):
     if args.heads:
         import dataclasses
         shape = dataclasses.replace(shape, heads=args.heads, name=shape.name + f"_heads{args.heads}")
+    wide = bool(args.head_dim) and args.head_dim != 128
+    if args.head_dim:
+        import dataclasses
+        shape = dataclasses.replace(shape, head_dim=args.head_dim, name=shape.name + f"_D{args.head_dim}")
     H, L, D = shape.heads, shape.seq_len, shape.head_dim
     M = shape.n_groups
     # clustered bf16 tensors -> top-mass indices (bf16 anchor-step kernels) -> per-head e4m3 quantisation
@@ -878,7 +882,10 @@ def run_fp8(args):
     gi = torch.empty(1, H, M, shape.topk, dtype=torch.int32, device=dev)
     for h0 in range(0, H, hc):
         q, k, v = synth.clustered_qkv(shape, heads=hc, head_offset=h0, device=dev)
-        gi[:, h0:h0 + hc] = synth.topmass_indices(q, k, shape)
+        if wide:     # (the group-mass kernel exists for head dimensions 64 and 128 only)
+            gi[:, h0:h0 + hc] = synth.random_sorted_indices(1, hc, M, shape.topk, L, seed=3 + h0, device=dev)
+        else:
+            gi[:, h0:h0 + hc] = synth.topmass_indices(q, k, shape)
         for dst, sc, t in ((q8, sq, q), (k8, sk, k), (v8, sv, v)):
             t8, s_ = synth.quantize_e4m3_per_head(t)
             dst[:, :, h0:h0 + hc] = t8
@@ -934,7 +941,9 @@ def run_fp8(args):
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "e4m3", "data": "synthetic",
         "config": {"workload": shape.name, "B": 1, "H": H, "L": L, "D": D, "groups": M, "topk": shape.topk,
-                   "residual": "fused", "indices": f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass (bf16 anchor pass), ascending",
+                   "residual": "fused",
+                   "indices": (f"4 sinks + {shape.topk - 4} random tokens, ascending" if wide else
+                               f"4 sinks + top-{shape.topk - 4} by exact fp32 group mass (bf16 anchor pass), ascending"),
                    "quantisation": "per head, scale = amax / 448",
                    "l2": f"inputs ({(3 * q8.numel() + 2 * out.numel() * 2 + gi.numel() * 4) / 1e9:.2f} GB per call) larger than L2; no explicit flush"},
         "clocks": clocks, "gpu_launches": args.steps,
@@ -944,7 +953,8 @@ def run_fp8(args):
                      "frac": achieved / peak["fp8_tflops"], "frac_of_sustained": achieved / peak["fp8_tflops_sustained"],
                      "frac_of_2x_bf16_burst": achieved / (2 * bf16["bf16_tflops"]), "traffic": None,
                      "peak_source": "measured in this run: " + peak["how"], "peak_sustained": peak["fp8_tflops_sustained"],
-                     "kernel": "gather_attn_kernel<128,e4m3>", "algorithmic_flops_per_launch": flops,
+                     "kernel": f"gather_attn_wide_kernel<{(D + 127) // 128},e4m3>" if wide else "gather_attn_kernel<128,e4m3>",
+                     "algorithmic_flops_per_launch": flops,
                      "algorithmic_bytes_per_launch": 3 * q8.numel() + 2 * out.numel() * 2 + gi.numel() * 4},
     }
     if check is not None:

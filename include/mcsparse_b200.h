@@ -90,7 +90,7 @@ typedef struct mcs_gather_attn_args {
   int64_t v_stride[3];
   int64_t o_stride[3];
   int64_t r_stride[3];  /* batch, head, row (elements) */
-  int32_t B, Sq, Sk, H, D;  /* D: 16-bit types: a multiple of 8 up to 256 (64 and 128 on the persistent kernel); e4m3: 128 */
+  int32_t B, Sq, Sk, H, D;  /* D: 16-bit types: a multiple of 8 up to 256 (64 and 128 on the persistent kernel); e4m3: a multiple of 16 up to 256 (128 on the persistent kernel) */
   int32_t gather_len;   /* multiple of 128 */
   int32_t group_rows;   /* query rows per group, 1..128 (reference: 128) */
   int32_t dtype;        /* MCS_DTYPE_* */
