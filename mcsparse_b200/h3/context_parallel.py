@@ -402,10 +402,8 @@ def _make_kernel(kind: str, cfg: dict, dense: Callable) -> Callable:
                      "calibrate_steps", "pca_reorder", "pca_pow_iters", "pca_proj_dim", "bias_correction", "selection_mode",
                      "topp", "adaptive_layers", "use_chunk_selector", "chunk_selector_size", "offload_indices",
                      "cache_offload", "offload_prefetch_ahead", "update_steps", "approx_steps", "full_attn_impl",
-                     "allow_no_sink", "min_seq_len", "ticks_per_step")
+                     "allow_no_sink", "min_seq_len", "ticks_per_step", "cfg_slots")
             kw = {k: cfg[k] for k in known if k in cfg}
-            kw.setdefault("sink_tokens", 0)
-            kw.setdefault("topk", 0.25)
             inner = tsd.make_mcsa_token_dispatch(lambda q, k, v, *a, **k2: dense(q, k, v), **kw)
 
         def kernel(q, k, v, out_peers=None):

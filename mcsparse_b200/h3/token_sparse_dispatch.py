@@ -44,7 +44,8 @@ _STATS = {
     "sink_tokens": 0, "seq_len": 0, "batch": 0, "nominal_density": 0.0, "effective_density": 0.0,
 }
 _CONFIG_STATS = ("sink_tokens", "nominal_density")
-_CTX = {"ctx": None, "layer_cursor": 0, "sparse_seq_len": None, "seen_seq_lens": {}, "tick": 0, "ticks_per_step": 1}
+_CTX = {"ctx": None, "layer_cursor": 0, "sparse_seq_len": None, "seen_seq_lens": {}, "tick": 0, "ticks_per_step": 1,
+        "cfg_slots": ()}
 
 
 def get_mcsa_token_stats() -> dict:
@@ -79,6 +80,10 @@ def mcsa_token_begin_forward() -> None:
         _CTX["ctx"].step()
     _CTX["layer_cursor"] = 0
     _STATS["steps_ticked"] = (_CTX["tick"] - 1) // _CTX["ticks_per_step"] + 1
+    # forwards that alternate within a step (serial classifier-free guidance) each get their own cache slot (:306-309)
+    slots = _CTX["cfg_slots"]
+    if slots and hasattr(_CTX["ctx"], "use_slot"):
+        _CTX["ctx"].use_slot(slots[(_CTX["tick"] - 1) % len(slots)])
 
 
 # ------------------------------------------------------------------------------------------------ schedule
@@ -149,11 +154,16 @@ def effective_density(*, sink_tokens: int, seq_len: int, topk: float, tile_n: in
 
 
 # --------------------------------------------------------------------------------------------- eligibility
-def check_eligibility(*, ndim, is_cuda, dtype_ok, shapes_match, head_dim, seq_len_q, seq_len_k, has_attn_mask, is_causal,
-                      dropout_p, enable_gqa, scale, min_seq_len, sparse_seq_len, has_parallel_config=False,
-                      sink_tokens=0):
+def check_eligibility(*, ndim, is_cuda, dtype_is_bf16=None, shapes_match, head_dim, seq_len_q, seq_len_k, has_attn_mask,
+                      is_causal, dropout_p, enable_gqa, has_parallel_config=False, scale=None, sink_tokens=0,
+                      sparse_seq_len=None, min_seq_len=DEFAULT_MIN_SEQ_LEN, discovering=False, dtype_ok=None):
     """(ok, reason, severity).  "fallback": the kernel cannot express the call, the original dispatch serves it;
-    "raise": the configuration itself is wrong (:696-772).  Any softmax scale is supported by the kernels."""
+    "raise": the configuration itself is wrong (:696-772).  Parameter names as the reference's; ``dtype_is_bf16`` says
+    whether the dtype is one the kernels take (bf16, and here also fp16; ``dtype_ok`` is a synonym).  Any softmax
+    scale is supported by the kernels, so ``scale`` never disqualifies a call.  ``discovering``: no sparse call has
+    run yet, so a strictly longer sequence length may still replace the one committed to (:747-761)."""
+    if dtype_ok is None:
+        dtype_ok = bool(dtype_is_bf16)
     if has_parallel_config:
         # sequence shards: neither a global selection nor a [0, P) sink range means anything on 1/N of the tokens
         return False, "parallel_config is not None (context parallelism)", "fallback"
@@ -174,7 +184,9 @@ def check_eligibility(*, ndim, is_cuda, dtype_ok, shapes_match, head_dim, seq_le
     if seq_len_q < max(min_seq_len, BLKQ):
         return False, f"sequence length {seq_len_q} below the sparse floor {max(min_seq_len, BLKQ)}", "fallback"
     if sparse_seq_len is not None and seq_len_q != sparse_seq_len:
-        return False, "a second long sequence length: only the first one is sparsified", "fallback"
+        if not (discovering and seq_len_q > sparse_seq_len):
+            return False, (f"L={seq_len_q} is a second long sequence length (already committed to {sparse_seq_len}): "
+                           "only one length is sparsified"), "fallback"
     if sink_tokens >= seq_len_k:
         return False, f"sink_tokens={sink_tokens} >= L_k={seq_len_k}: nothing would be sparse", "raise"
     return True, "", ""
@@ -182,16 +194,17 @@ def check_eligibility(*, ndim, is_cuda, dtype_ok, shapes_match, head_dim, seq_le
 
 # ------------------------------------------------------------------------------------------------- factory
 def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 0, num_layers: Optional[int] = None,
-                             num_steps: int = DEFAULT_NUM_STEPS, topk: float = 0.15, dense_steps: int = 0,
-                             dense_layers="", calibrate_every: int = DEFAULT_CALIBRATE_EVERY,
-                             calibrate_steps: Optional[Sequence[int]] = (0,), pca_reorder: bool = True,
+                             num_steps: int = DEFAULT_NUM_STEPS, topk: float = DEFAULT_TOPK,
+                             dense_steps: int = DEFAULT_DENSE_STEPS, dense_layers=DEFAULT_DENSE_LAYERS,
+                             calibrate_every: int = DEFAULT_CALIBRATE_EVERY,
+                             calibrate_steps: Optional[Sequence[int]] = DEFAULT_CALIBRATE_STEPS, pca_reorder: bool = True,
                              pca_pow_iters: int = 4, pca_proj_dim=None, bias_correction: bool = True,
                              selection_mode: str = "topk", topp: Optional[float] = None, adaptive_layers: bool = False,
                              use_chunk_selector: bool = False, chunk_selector_size: int = 16384,
                              offload_indices: bool = False, cache_offload: str = "none", offload_prefetch_ahead: int = 1,
                              update_steps: Optional[Sequence[int]] = None, approx_steps: Optional[Sequence[int]] = None,
-                             full_attn_impl: str = "native", allow_no_sink: bool = True,
-                             min_seq_len: int = 1024, ticks_per_step: int = 1,
+                             full_attn_impl: str = "native", allow_no_sink: bool = False,
+                             min_seq_len: int = DEFAULT_MIN_SEQ_LEN, ticks_per_step: int = 1, cfg_slots=(),
                              full_steps: Optional[Sequence[int]] = None, full_layers: Sequence[int] = (),
                              sink_ranges=None, context=None) -> Callable:
     """Build the dispatch function (argument names and meaning as the reference's factory, :778-808).
@@ -202,8 +215,11 @@ def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 
     ``full_steps`` / ``full_layers`` / ``sink_ranges`` may instead be given directly.  ``context`` may inject a
     ready TokenSparseContext-like object (``forward(li, q, k, v, scale)``, ``caches[li].mode``, ``step()``,
     ``reset()``), which the CPU tests use.  ``offload_indices`` / ``cache_offload`` / ``offload_prefetch_ahead`` park
-    indices / residual in pinned host memory between uses (default off); ``full_attn_impl`` is accepted for call
-    compatibility and has no effect: there is one dense implementation.
+    indices / residual in pinned host memory between uses (default off, where the reference's factory defaults to on:
+    a 180 GB part keeps them resident); ``full_attn_impl`` is accepted for call compatibility and has no effect: there
+    is one dense implementation.  ``ticks_per_step`` forwards make one denoising step, and ``cfg_slots`` (e.g.
+    ``("cond", "uncond")``) gives each of them its own cache slot (:840-851).  The other defaults are the reference's
+    (``DEFAULT_*``; ``sink_tokens`` is required there and 0 is refused without ``allow_no_sink=True``, as here).
     """
     sink_tokens = int(sink_tokens)
     if sink_tokens < 0:
@@ -255,6 +271,9 @@ def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 
         _CTX["ctx"].reset()                                       # release the previous context's caches first
     _CTX["ctx"] = context
     _CTX["ticks_per_step"] = max(1, int(ticks_per_step))
+    _CTX["cfg_slots"] = tuple(cfg_slots)
+    if _CTX["cfg_slots"] and _CTX["ticks_per_step"] % len(_CTX["cfg_slots"]):
+        raise ValueError(f"cfg_slots={cfg_slots!r} needs ticks_per_step to be a multiple of {len(_CTX['cfg_slots'])}")
     reset_mcsa_token_state()
     _STATS["nominal_density"] = float(topk)
     _STATS["sink_tokens"] = sink_tokens
@@ -297,13 +316,21 @@ def make_mcsa_token_dispatch(original_dispatch: Callable, *, sink_tokens: int = 
             seq_len_k=key.shape[1] if getattr(key, "ndim", 0) == 4 else -1, has_attn_mask=attn_mask is not None,
             is_causal=bool(is_causal), dropout_p=float(dropout_p or 0.0), enable_gqa=bool(enable_gqa), scale=scale,
             min_seq_len=min_seq_len, sparse_seq_len=_CTX["sparse_seq_len"],
-            has_parallel_config=parallel_config is not None, sink_tokens=sink_tokens)
+            has_parallel_config=parallel_config is not None, sink_tokens=sink_tokens,
+            discovering=_STATS["kernel_calls"] == 0)
         if not ok:
             if severity == "raise":
                 raise RuntimeError(f"[mcsa-token] {reason}")
             _STATS["fallback_calls"] += 1                         # consumes no layer index
             return _dense()
         B, T, H, D = query.shape
+        if _CTX["sparse_seq_len"] is not None and T > _CTX["sparse_seq_len"]:
+            # a longer eligible call inside the discovery window (no sparse call has run, so no cache exists): it
+            # replaces the provisional length, and the layer numbering of this forward starts over (:350-380)
+            print(f"[mcsa-token] sparse length {_CTX['sparse_seq_len']} -> {T}: a longer eligible call appeared before the "
+                  "first sparse call", file=sys.stderr, flush=True)
+            _CTX["sparse_seq_len"] = None
+            _CTX["layer_cursor"] = 0
         if _CTX["sparse_seq_len"] is None:
             _CTX["sparse_seq_len"] = T
             _STATS["seq_len"], _STATS["batch"] = T, B

@@ -9,6 +9,7 @@ that sit on the accelerated path; the compute runs in the CUDA library through t
 
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional
 
@@ -324,7 +325,6 @@ class TokenSparseConfig:
     sink_ranges: Optional[List[Tuple[int, int]]] = None
     calibrate_steps: Optional[List[int]] = None
     update_steps: Optional[List[int]] = None
-    approx_steps: Optional[List[int]] = None
     full_steps: Optional[List[int]] = None
     full_layers: List[int] = field(default_factory=list)
     share_lse: bool = False
@@ -333,13 +333,17 @@ class TokenSparseConfig:
     adaptive_layers: bool = False
     use_chunk_selector: bool = False
     chunk_selector_size: int = 16384
+    offload_indices: bool = False          # keep the indices in pinned host memory between uses
+    approx_steps: Optional[List[int]] = None
     bias_correction: bool = False
+    cache_offload: str = 'none'            # 'residual': the same for the bias-correction residual
+    full_attn_impl: str = 'sdpa'           # accepted for call compatibility: there is one dense implementation here
     pca_reorder: bool = False
     pca_pow_iters: int = 4
-    pca_seed: int = 0
     pca_proj_dim: Optional[int] = None
-    offload_indices: bool = False          # keep the indices in pinned host memory between uses (reference default: True)
-    cache_offload: str = 'none'            # 'residual': the same for the bias-correction residual
+    pca_whiten: bool = False
+    # additions of this package (after the reference's fields, so positional construction keeps its meaning)
+    pca_seed: int = 0
     offload_prefetch_ahead: int = 1        # layers ahead of its use at which an offloaded tensor starts to come back
     compact_indices: bool = False          # keep the cached indices in the packed 17-bit form (sequences up to 131,072 keys)
 
@@ -357,8 +361,8 @@ class TokenSparseConfig:
             ds = (int(self.cal_downsample),) * 2
         if ds != (1, 1):
             raise NotImplementedError("cal_downsample > 1 is not part of the accelerated path")
-        if self.pca_proj_dim is not None:
-            raise NotImplementedError("pca_proj_dim is not part of the accelerated path")
+        if self.pca_proj_dim is not None or self.pca_whiten:
+            raise NotImplementedError("pca_proj_dim / pca_whiten are not part of the accelerated path")
         self._cal_ds_q, self._cal_ds_k = ds
         self._calibrate_set = set(self.calibrate_steps) if self.calibrate_steps else None
         self._update_set = set(self.update_steps) if self.update_steps else None
@@ -604,13 +608,21 @@ class TokenSparseBackend:
 
 class TokenSparseContext:
     """All layers of a model: one cache per layer, one step clock (token_sparse.py:1461-1845).  Without
-    ``num_layers`` the caches are created as layers show up (``cache(li)``)."""
+    ``num_layers`` the caches are created as layers show up (``cache(li)``).
+
+    Named cache slots (``cache_context`` / ``use_slot``, token_sparse.py:1581-1612) keep separate per-layer caches
+    for forwards that alternate within one denoising step (serial classifier-free guidance: a conditional and an
+    unconditional pass), so that one pass's anchor step does not overwrite the other's selection; all slots share
+    the step clock."""
 
     def __init__(self, config: TokenSparseConfig, num_layers: Optional[int] = None):
         self.config = config
         self.backend = TokenSparseBackend(config)
         self._nl = num_layers
+        self._sc = 0
         self.caches: List[TokenSparseCache] = []
+        self._cache_slots = {"_default": self.caches}
+        self._active_slot = "_default"
         for i in range(num_layers or 0):
             self.cache(i)
 
@@ -618,8 +630,29 @@ class TokenSparseContext:
         while len(self.caches) <= li:
             i = len(self.caches)
             t = i / max(self._nl - 1, 1) if (self._nl and self.config.adaptive_layers) else None
-            self.caches.append(TokenSparseCache(self.config, i, t))
+            c = TokenSparseCache(self.config, i, t)
+            c._step_count = self._sc                    # a cache that shows up later joins the common clock
+            self.caches.append(c)
         return self.caches[li]
+
+    def use_slot(self, name: str) -> None:
+        """Make ``name`` the active cache slot (created empty on first use)."""
+        if name not in self._cache_slots:
+            self._cache_slots[name] = []
+        self._active_slot = name
+        self.caches = self._cache_slots[name]
+        for i in range(self._nl or 0):
+            self.cache(i)
+
+    @contextlib.contextmanager
+    def cache_context(self, name: str):
+        """Activate a named cache slot for the duration of one forward and restore the previous one afterwards."""
+        prev = self._active_slot
+        self.use_slot(name)
+        try:
+            yield
+        finally:
+            self.use_slot(prev)
 
     def forward(self, li: int, q, k, v, scale: Optional[float] = None, out_peers=None):
         if self.config.offload_prefetch_ahead and li + 1 < len(self.caches):
@@ -628,8 +661,13 @@ class TokenSparseContext:
             return dense_attention_with_lse(q, k, v, scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))[0]
         return self.backend.forward(self.cache(li), q, k, v, scale, out_peers=out_peers)
 
+    def _all_caches(self):
+        for slot in self._cache_slots.values():
+            yield from slot
+
     def step(self) -> None:
-        for c in self.caches:
+        self._sc += 1
+        for c in self._all_caches():
             c.step()
         if self.caches and self.config.offload_prefetch_ahead:
             self.caches[0].prefetch()                   # the first layer of the next step has no layer in front of it
@@ -638,13 +676,16 @@ class TokenSparseContext:
             _lib.poll_status(torch.cuda.current_device(), "TokenSparseContext.step")
 
     def reset(self) -> None:
-        for c in self.caches:
+        self._sc = 0
+        for c in self._all_caches():
             c.reset()
+        self.caches = self._cache_slots["_default"]
+        self._active_slot = "_default"
 
     def offload_stats(self) -> dict:
         """Prefetch hits and misses over all layers: a miss is a use that had to copy on its own stream."""
         out = {"idx_prefetch_hit": 0, "idx_prefetch_miss": 0, "res_prefetch_hit": 0, "res_prefetch_miss": 0}
-        for c in self.caches:
+        for c in self._all_caches():
             for k, v in c.offload_stats().items():
                 out[k] += v
         return out

@@ -95,6 +95,11 @@ class FakeTensor:
         return self
 
 
+# the factory's defaults are the reference's (10 dense steps, dense layers 0-1, anchor at step 9, sink required, floor
+# 4096); the dispatch tests below want every step sparse from step 0
+_PLAIN = dict(allow_no_sink=True, dense_steps=0, dense_layers="", calibrate_steps=(0,), min_seq_len=1024)
+
+
 def test_dispatch_counters_and_layer_clock():
     ctx = FakeCtx(3)
     calls = []
@@ -103,8 +108,8 @@ def test_dispatch_counters_and_layer_clock():
         calls.append(q.shape[1])
         return "dense"
 
-    d = tsd.make_mcsa_token_dispatch(original, num_layers=3, topk=0.15, full_layers=[2], min_seq_len=1024, context=ctx,
-                                     sink_ranges=[(0, 4)])
+    d = tsd.make_mcsa_token_dispatch(original, num_layers=3, topk=0.15, full_layers=[2], context=ctx,
+                                     sink_ranges=[(0, 4)], **_PLAIN)
     long_ = FakeTensor((1, 2048, 2, 128))
     short = FakeTensor((1, 77, 2, 128))
     for step in range(2):
@@ -131,9 +136,9 @@ def test_dispatch_counters_and_layer_clock():
 
 def test_dispatch_guards():
     with pytest.raises(RuntimeError):
-        tsd.make_mcsa_token_dispatch(lambda *a, **k: None, num_layers=2, topk=1.5, context=FakeCtx(2))
+        tsd.make_mcsa_token_dispatch(lambda *a, **k: None, num_layers=2, topk=1.5, context=FakeCtx(2), **_PLAIN)
     ctx = FakeCtx(1)
-    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx)
+    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx, **_PLAIN)
     t = FakeTensor((1, 2048, 2, 128))
     tsd.mcsa_token_begin_forward()
     d(t, t, t)
@@ -196,7 +201,7 @@ def test_parallel_config_falls_back_and_sink_splice():
         seen.append((tuple(q.shape), kw.get("parallel_config")))
         return torch.ones(q.shape, dtype=torch.bfloat16)
 
-    d = tsd.make_mcsa_token_dispatch(original, num_layers=1, topk=0.15, sink_tokens=8, min_seq_len=1024, context=ctx)
+    d = tsd.make_mcsa_token_dispatch(original, num_layers=1, topk=0.15, sink_tokens=8, context=ctx, **_PLAIN)
     t = FakeTensor((1, 2048, 2, 128))
     tsd.mcsa_token_begin_forward()
     pc = _Cfg(context_parallel_config=_Cfg(ulysses_degree=2, ring_degree=1))
@@ -218,9 +223,9 @@ def test_parallel_config_falls_back_and_sink_splice():
     with pytest.raises(ValueError):
         tsd.make_mcsa_token_dispatch(original, num_layers=1, sink_tokens=0, allow_no_sink=False, context=FakeCtx(1))
     with pytest.raises(ValueError):
-        tsd.make_mcsa_token_dispatch(original, num_layers=1, sink_tokens=4, use_chunk_selector=True, context=FakeCtx(1))
+        tsd.make_mcsa_token_dispatch(original, num_layers=1, sink_tokens=4, use_chunk_selector=True, context=FakeCtx(1), **_PLAIN)
     with pytest.raises(ValueError):
-        tsd.make_mcsa_token_dispatch(original, num_layers=1, cache_offload="residual", bias_correction=False, context=FakeCtx(1))
+        tsd.make_mcsa_token_dispatch(original, num_layers=1, cache_offload="residual", bias_correction=False, context=FakeCtx(1), **_PLAIN)
 
 
 def test_kernel_problem_is_counted_and_served_densely():
@@ -230,7 +235,7 @@ def test_kernel_problem_is_counted_and_served_densely():
         def forward(self, li, q, k, v, scale):
             raise _lib.KernelStatusError("kernel status 30")
 
-    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=Failing(1))
+    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=Failing(1), **_PLAIN)
     t = FakeTensor((1, 2048, 2, 128))
     tsd.mcsa_token_begin_forward()
     assert d(t, t, t) == "dense"
@@ -241,7 +246,7 @@ def test_kernel_problem_is_counted_and_served_densely():
 
 def test_ticks_per_step():
     ctx = FakeCtx(1)
-    tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx, ticks_per_step=2)
+    tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx, ticks_per_step=2, **_PLAIN)
     for _ in range(6):
         tsd.mcsa_token_begin_forward()
     assert ctx.steps == 2 and tsd.get_mcsa_token_stats()["steps_ticked"] == 3
@@ -283,3 +288,69 @@ def test_with_ulysses_sparse_truth_table():
         d.forward_op(None, t, t, t, return_lse=True)
     cp.reset_cp_stats()
     assert cp.get_cp_stats() == {"cp_calls": 0, "local_calls": 0}
+
+
+def test_cfg_slots_give_each_forward_of_a_step_its_own_cache_slot():
+    """Serial classifier-free guidance: two forwards per step, each with its own cache slot (reference :306-309, :840-851)."""
+    class SlotCtx(FakeCtx):
+        def __init__(self, n):
+            super().__init__(n)
+            self.slots = []
+
+        def use_slot(self, name):
+            self.slots.append(name)
+
+    ctx = SlotCtx(1)
+    tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=ctx, ticks_per_step=2,
+                                 cfg_slots=("cond", "uncond"), **_PLAIN)
+    for _ in range(5):
+        tsd.mcsa_token_begin_forward()
+    assert ctx.slots == ["cond", "uncond", "cond", "uncond", "cond"] and ctx.steps == 2
+    with pytest.raises(ValueError):
+        tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=1, context=SlotCtx(1), ticks_per_step=3,
+                                     cfg_slots=("cond", "uncond"), **_PLAIN)
+
+
+def test_discovery_window_lets_a_longer_sequence_replace_the_first_one():
+    """Until the first sparse call has run, a strictly longer eligible call replaces the committed length (the
+    reference's _maybe_upgrade_seq_len, :338-380); afterwards a second long length is left dense."""
+    ctx = FakeCtx(2)
+    ctx.caches[0].mode = "full"                   # the first layer is a dense-guard layer: no sparse call yet
+    d = tsd.make_mcsa_token_dispatch(lambda *a, **k: "dense", num_layers=2, context=ctx, **_PLAIN)
+    tsd.mcsa_token_begin_forward()
+    refiner, packed, longer = FakeTensor((1, 2048, 2, 128)), FakeTensor((1, 8192, 2, 128)), FakeTensor((1, 16384, 2, 128))
+    assert d(refiner, refiner, refiner) == "dense"                # eligible, dense guard: commits to 2048 provisionally
+    assert tsd.get_mcsa_token_stats()["seq_len"] == 2048 and tsd.get_mcsa_token_stats()["kernel_calls"] == 0
+    assert d(packed, packed, packed) == "dense"                   # longer, still discovering: replaces it, layer 0 again
+    s = tsd.get_mcsa_token_stats()
+    assert s["seq_len"] == 8192 and s["dense_guard_calls"] == 2 and s["fallback_calls"] == 0
+    out = d(packed, packed, packed)                               # layer 1: the first sparse call
+    assert torch.is_tensor(out) and tsd.get_mcsa_token_stats()["kernel_calls"] == 1
+    assert d(refiner, refiner, refiner) == "dense"                # the shorter length now falls back ...
+    assert d(longer, longer, longer) == "dense"                   # ... and so does a longer one: the window is closed
+    s = tsd.get_mcsa_token_stats()
+    assert s["fallback_calls"] == 2 and s["seq_len"] == 8192
+    ok, reason, sev = tsd.check_eligibility(ndim=4, is_cuda=True, dtype_is_bf16=True, shapes_match=True, head_dim=128,
+                                            seq_len_q=9000, seq_len_k=9000, has_attn_mask=False, is_causal=False,
+                                            dropout_p=0.0, enable_gqa=False, has_parallel_config=False, scale=None,
+                                            sink_tokens=0, sparse_seq_len=8192, min_seq_len=4096, discovering=True)
+    assert ok and not reason
+
+
+def test_context_cache_slots_share_the_step_clock():
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
+    ctx = TokenSparseContext(TokenSparseConfig(topk=0.1, calibrate_steps=[0, 4]), num_layers=2)
+    default = list(ctx.caches)
+    ctx.step(); ctx.step(); ctx.step()
+    with ctx.cache_context("uncond"):
+        assert len(ctx.caches) == 2 and all(a is not b for a, b in zip(ctx.caches, default))
+        assert [c._step_count for c in ctx.caches] == [3, 3]          # a slot that shows up later joins the clock
+        uncond = list(ctx.caches)
+    assert ctx.caches == default and ctx._active_slot == "_default"
+    ctx.step()
+    assert [c._step_count for c in default + uncond] == [4, 4, 4, 4]
+    assert uncond[0].mode == "calibrate"                               # step 4 is an anchor step in every slot
+    ctx.use_slot("uncond")
+    assert ctx.caches == uncond
+    ctx.reset()
+    assert ctx.caches == default and [c._step_count for c in default + uncond] == [0, 0, 0, 0]

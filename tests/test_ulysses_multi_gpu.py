@@ -67,8 +67,8 @@ def _worker(rank, world, port, q):
         #          (rows stored straight into the owners' shards) == the plain dispatch on one GPU
         dense = cp._make_dense(False)
         orig = lambda q_, k_, v_, *a, **kw: dense(q_, k_, v_)
-        common = dict(num_layers=1, topk=0.125, sink_tokens=0, calibrate_steps=(0,), pca_reorder=True, bias_correction=True,
-                      min_seq_len=1024)
+        common = dict(num_layers=1, topk=0.125, sink_tokens=0, allow_no_sink=True, dense_steps=0, dense_layers="",
+                      calibrate_steps=(0,), pca_reorder=True, bias_correction=True, min_seq_len=1024)
         outs_single = []
         d1 = tsd.make_mcsa_token_dispatch(orig, **common)
         for step in range(3):
