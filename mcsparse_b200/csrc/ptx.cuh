@@ -366,6 +366,17 @@ __device__ __forceinline__ float ex2_poly3_scaled(float x, float c, float xmin) 
   p = fmaf(p, f, 0.9999281764030457f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+// 2^y without the special-function unit, to the precision an e4m3 probability needs (quadratic, largest relative
+// error 1.7e-3 against e4m3's half-step of 3e-2): the same construction as ex2_poly3_scaled on an argument that is
+// already in the log2 domain; anything below 2^-100 comes out as 2^-100 (zero after quantisation).
+__device__ __forceinline__ float ex2_poly2(float y) {
+  y = fmaxf(y, -100.f);
+  const float t = y + 12582912.f;
+  const float f = y - (t - 12582912.f);
+  float p = fmaf(0.23842892050743103f, f, 0.7034479975700378f);
+  p = fmaf(p, f, 1.0004431009292603f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
