@@ -219,7 +219,7 @@ int mcs_group_mass(const mcs_group_mass_args* a, void* stream) {
   if (a->B < 1 || a->H < 1 || a->Lq < 1 || a->Lk < 1) return MCS_ERR_BAD_SHAPE;
   if (a->group_rows < 1 || a->group_rows > 128) return MCS_ERR_BAD_SHAPE;
   if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
-  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  if (a->D < 8 || a->D > 256 || a->D % 8 != 0) return MCS_ERR_BAD_HEAD_DIM;   // 64 and 128 native, others on padded layouts
   if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return MCS_ERR_BAD_SCALE;
   if (!aligned16(a->q) || !aligned16(a->k)) return MCS_ERR_BAD_ALIGNMENT;
   for (int i = 0; i < 3; ++i)

@@ -51,20 +51,25 @@ enum { BAR_FULL = 0, BAR_EMPTY = BAR_FULL + kRing, BAR_Q_FULL = BAR_EMPTY + kRin
        BAR_PART = BAR_S_FREE + 2,      // [4 lane groups][2 bufs]: partial sums of the upper column half are in shared memory
        BAR_DRAIN = BAR_PART + 8, BAR_COUNT };
 
+// D is the head dimension rounded up to the tile layouts this kernel has: 64, 128, 192 or 256 (the true head
+// dimension, any multiple of 8 up to 256, is a run-time value; rows are zero-padded on their way into shared memory)
 template <int D>
 struct Smem {
   static constexpr int kBlocks = D / 64;
   static constexpr int kTileBytes = kBlocks * 16384;
+  static constexpr int kRingN = D == 256 ? 2 : kRing;        // key-tile slots that fit beside the query tile
   static constexpr int kQ = 0;                              // group's query rows (B operand)
   static constexpr int kQx = kTileBytes;                    // extra k-step of Q: 128 rows x 128 B (first 32 B used)
   static constexpr int kKx = kQx + 16384;                   // extra k-step of K: constant (1,1,1,0...)
   static constexpr int kRingOff = kKx + 16384;
-  static constexpr int kBars = kRingOff + kRing * kTileBytes;
+  static constexpr int kBars = kRingOff + kRingN * kTileBytes;
   static constexpr int kPart = kBars + BAR_COUNT * 8;       // float [2][128]: partial sums of the upper column half
   static constexpr int kTmemSlot = kPart + 2 * 128 * 4;
   static constexpr int kTotal = kTmemSlot + 16;
   static constexpr int kDynamic = kTotal + 1024;
 };
+
+static_assert(Smem<192>::kDynamic <= 232448 && Smem<256>::kDynamic <= 232448, "padded layouts must fit 227 KB");
 
 __device__ __forceinline__ uint32_t swz(int row, int c) {   // 16-byte chunk c of row, 128-byte swizzle
   return static_cast<uint32_t>((c >> 3) * 16384 + row * 128 + (((c & 7) ^ (row & 7)) << 4));
@@ -75,6 +80,9 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
   // key tiles are 128 consecutive rows: with a valid tensor map one elected thread loads them by TMA
   const bool use_tma = kmap.valid != 0;
   using L = Smem<D>;
+  constexpr bool kWide = D > 128;                       // padded layouts: the true head dimension is p.D < D
+  constexpr int R = L::kRingN;
+  const int d_chunks = p.D / 8;                          // 16-byte chunks of a real row
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
@@ -93,7 +101,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
   const int n_tiles = (p.Lk + kTile - 1) / kTile;
 
   if (tid == 0) {
-    for (int i = 0; i < kRing; ++i) {
+    for (int i = 0; i < R; ++i) {
       mbar_init(bar(BAR_FULL + i), use_tma ? 1 : kProducerThreads);
       mbar_init(bar(BAR_EMPTY + i), 1);
     }
@@ -201,17 +209,27 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
         tc_fence_after();
         const uint32_t tS = tmem + buf * 128;
         const uint32_t klo = ((sRing(slot) & 0x3FFFFu) >> 4) | kLbo;
+        if constexpr (kWide) {
+          // the k-steps that hold real columns (the last one zero-padded to 16)
+          const int ksteps = (p.D + 15) / 16;
+#pragma unroll 1
+          for (int j = 0; j < ksteps; ++j) {
+            const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
+            if (leader) mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);
+          }
+        } else {
 #pragma unroll
-        for (int j = 0; j < D / 16; ++j) {
-          const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
-          if (leader) mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);     // A = K tile, B = Q group
+          for (int j = 0; j < D / 16; ++j) {
+            const uint32_t koff = (j >> 2) * (16384 >> 4) + (j & 3) * 2;
+            if (leader) mma_f16_ss(tS, desc(klo + koff), desc(qlo + koff), idesc, j > 0);     // A = K tile, B = Q group
+          }
         }
         if (leader) {
           mma_f16_ss(tS, desc(kxlo), desc(qxlo), idesc, 1);                     // extra k-step: - lse / scale
           tc_commit(bar(BAR_EMPTY + slot));
           tc_commit(bar(BAR_S_FULL + buf));
         }
-        if (++slot == kRing) { slot = 0; phase ^= 1; }
+        if (++slot == R) { slot = 0; phase ^= 1; }
       }
       if (!ok) {
         if (leader) tc_commit(bar(BAR_DRAIN));
@@ -225,9 +243,13 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
     const int pw = warp - kProducerWarp0;
     const int ptid = pw * 32 + lane;                    // 0..127: also the row this thread prepares
     const int row0 = pw * 32;
-    constexpr int kChunks = D / 8;
+    // one lane per 16-byte chunk of a row; the padded layouts give every lane one of 32 chunk positions, of which
+    // D / 8 exist in the tile (the others idle) and p.D / 8 hold data (the rest is zero-filled)
+    constexpr int kChunks = kWide ? 32 : D / 8;
     constexpr int kRowsPerInstr = 32 / kChunks;
     const int sub = lane / kChunks, cch = lane % kChunks;
+    const bool c_in_tile = !kWide || cch < D / 8;
+    const bool c_live = !kWide || cch < d_chunks;
     // ---- constant extra K block, extra Q block, Q rows
     {
       // K extra: every row (1, 1, 1, 0, ...); Q extra: (-hi, -mid, -lo, 0, ...) of lse / scale
@@ -275,8 +297,10 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
         const int rl = i * kRowsPerInstr + sub;
         const int id = __shfl_sync(0xffffffffu, src, rl);
         const uint32_t dst = s_base + L::kQ + swz(row0 + rl, cch);
-        if (id >= 0) cp_async16(dst, qb + (size_t)id * q_row);
-        else cp_async16_zfill(dst, qb, 0);
+        if (c_in_tile) {
+          if (id >= 0 && c_live) cp_async16(dst, qb + (size_t)id * q_row);
+          else cp_async16_zfill(dst, p.q, 0);
+        }
       }
       cp_async_arrive_noinc(bar(BAR_Q_FULL));
     }
@@ -305,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
             for (int cb = 0; cb < L::kBlocks; ++cb)
               tma_load_4d(sRing(slot) + cb * 16384, kmap.k, cb * 64, co[1], co[2], co[3], bar(BAR_FULL + slot));
           }
-          if (++slot == kRing) { slot = 0; phase ^= 1; wrapped = true; }
+          if (++slot == R) { slot = 0; phase ^= 1; wrapped = true; }
         }
       }
       n_tiles_cp = 0;
@@ -320,11 +344,13 @@ __global__ void __launch_bounds__(kThreads, 1) group_mass_kernel(const GroupMass
         const int rl = row0 + i * kRowsPerInstr + sub;
         const int krow = t * kTile + rl;
         const uint32_t dst = dst0 + swz(rl, cch);
-        if (krow < p.Lk) cp_async16(dst, kb + (size_t)krow * k_row);
-        else cp_async16_zfill(dst, kb, 0);
+        if (c_in_tile) {
+          if (krow < p.Lk && c_live) cp_async16(dst, kb + (size_t)krow * k_row);
+          else cp_async16_zfill(dst, p.k, 0);
+        }
       }
       cp_async_arrive_noinc(bar(BAR_FULL + slot));
-      if (++slot == kRing) { slot = 0; phase ^= 1; wrapped = true; }
+      if (++slot == R) { slot = 0; phase ^= 1; wrapped = true; }
     }
     cp_async_wait_all();
   }
@@ -343,7 +369,8 @@ int launch(const GroupMassParams& p, cudaStream_t stream) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return -8;
   const long long grid = (long long)p.B * p.H * p.M;
   KeyTileMap kmap{};
-  kmap.valid = encode_tile_map(p.k, p.k_stride, p.B, p.Lk, p.H, D, kmap.k, kmap.pos_h, kmap.pos_row, kmap.pos_b);
+  // (the map carries the true head dimension: boxes that reach beyond it are zero-filled by the copy engine)
+  kmap.valid = encode_tile_map(p.k, p.k_stride, p.B, p.Lk, p.H, p.D, kmap.k, kmap.pos_h, kmap.pos_row, kmap.pos_b);
   kern<<<(unsigned)grid, kThreads, L::kDynamic, stream>>>(p, kmap);
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
@@ -353,7 +380,10 @@ int launch(const GroupMassParams& p, cudaStream_t stream) {
 int launch_group_mass(const GroupMassParams& p, bool fp16, cudaStream_t stream) {
   if (p.D == 128) return fp16 ? launch<128, true>(p, stream) : launch<128, false>(p, stream);
   if (p.D == 64) return fp16 ? launch<64, true>(p, stream) : launch<64, false>(p, stream);
-  return -3;
+  // every other multiple of 8 up to 256 (the reference's head-dimension table has 96, 144, 160, 192, 256): padded layouts
+  if (p.D < 8 || p.D > 256 || p.D % 8 != 0) return -3;
+  if (p.D <= 192) return fp16 ? launch<192, true>(p, stream) : launch<192, false>(p, stream);
+  return fp16 ? launch<256, true>(p, stream) : launch<256, false>(p, stream);
 }
 
 }  // namespace mcs

@@ -97,3 +97,29 @@ def test_mass_matches_reference_kernel_output(cuda_device):
         tp = _compute_token_probs(q.to(dev), k.to(dev), lse.to(dev), 128, scale)
         assert tp.dtype == q.dtype
         assert (tp.cpu().double() - ref).abs().max() / ref.abs().max() < (1e-2 if q.dtype == torch.bfloat16 else 3e-3)
+
+
+@pytest.mark.parametrize("D", [96, 144, 160, 192, 256, 32])
+def test_mass_other_head_dims(cuda_device, D):
+    """Head dimensions other than 64 and 128 (the reference's Triton kernel takes any; its head-dimension table lists
+    96, 144, 160, 192, 256): padded tile layouts, by TMA (contiguous keys) and by cp.async (keys shared by the heads),
+    with a permutation and ragged last group / last key tile."""
+    from mcsparse_b200.kernels.flash_mcsa.token_sparse import group_mass
+    B, H, L = 1, 2, 600
+    q, k = _clustered(B, H, L, D, 10 + D, torch.bfloat16)
+    g = torch.Generator().manual_seed(D)
+    perm = torch.stack([torch.randperm(L, generator=g) for _ in range(B * H)])
+    qp = torch.stack([q[0, h][perm[h]] for h in range(H)]).unsqueeze(0)
+    lse_p = dense_lse_ref(qp, k).float()
+    ref = group_mass_ref(q, k, lse_p, perm=perm)
+    dev = cuda_device
+    out = group_mass(q.to(dev), k.to(dev), lse_p.to(dev), perm=perm.to(dev)).cpu().double()
+    assert (out - ref).abs().max() / ref.abs().max() < 2e-3
+    # keys of head 0 shared by both heads: no tensor map, the cp.async route
+    k1 = k[:, :1]
+    lse1 = dense_lse_ref(q, k1.expand(B, H, L, D)).float()
+    ref1 = group_mass_ref(q, k1.expand(B, H, L, D).contiguous(), lse1)
+    kd = k1.to(dev).expand(B, H, L, D)
+    out1 = group_mass(q.to(dev), kd, lse1.to(dev)).cpu().double()
+    assert (out1 - ref1).abs().max() / ref1.abs().max() < 2e-3
+    assert torch.equal(out1, group_mass(q.to(dev), kd.contiguous(), lse1.to(dev)).cpu().double())
