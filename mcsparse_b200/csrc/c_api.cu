@@ -285,7 +285,7 @@ int mcs_pddp_perm(const mcs_pddp_args* a, void* stream) {
   if (a == nullptr || a->x == nullptr || a->perm_out == nullptr || a->workspace == nullptr || a->status == nullptr)
     return MCS_ERR_NULL_POINTER;
   if (a->BH < 1 || a->N < 1 || a->C < 1 || a->pow_iters < 0) return MCS_ERR_BAD_SHAPE;
-  if (a->D != 64 && a->D != 128) return MCS_ERR_BAD_HEAD_DIM;
+  if (a->D < 8 || a->D > 256 || a->D % 8 != 0) return MCS_ERR_BAD_HEAD_DIM;   // 64 / 128: tensor-core Gram path; others: Gram-free path
   if (a->dtype != MCS_DTYPE_BF16 && a->dtype != MCS_DTYPE_FP16) return MCS_ERR_BAD_DTYPE;
   if (!aligned16(a->x) || a->x_stride_bh % 8 || a->x_stride_row % 8) return MCS_ERR_BAD_ALIGNMENT;
   const size_t need = mcs::pddp_workspace_bytes(a->BH, a->N, a->C);

@@ -362,6 +362,189 @@ __global__ void __launch_bounds__(256) pddp_project_kernel(PddpParams p, int lv,
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Head dimensions other than 64 and 128 (multiples of 8 up to 256): the principal direction by power iterations
+// that never form the Gram matrix.  With t_r = x_r . v,
+//     (X^T X - s s^T / n) v  =  sum_r x_r t_r  -  s (sum_r t_r) / n,
+// so one pass over the node's rows per iteration gives the next vector.  The rows are read pow_iters times per level
+// instead of once, which is the price of staying clear of a 256 x 256 Gram matrix per node; this path serves the
+// uncommon head dimensions, the tensor-core Gram path above the common ones.  Partial sums of a node's chunks are
+// combined in chunk order by the next kernel: deterministic, no atomics.
+// ------------------------------------------------------------------------------------------
+constexpr int kWideD = 256;
+constexpr int kWideFloats = 2 * kWideD + 8;      // per chunk: sum_r x_r t_r [256], sum_r x_r [256], sum_r t_r
+
+__device__ __forceinline__ float block_sum_256(float x, float* red) {
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w];
+  return t;
+}
+
+// v = v0 / |v0| for every node of the level (zeros beyond D)
+__global__ void __launch_bounds__(256) pddp_wide_init_kernel(PddpParams p, int nodes, const float* v0, float* wdir) {
+  __shared__ float red[8];
+  const int node = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+  float v = d < p.D ? v0[((size_t)bh * nodes + node) * p.D + d] : 0.f;
+  const float nrm = sqrtf(block_sum_256(v * v, red));
+  wdir[((size_t)bh * p.dir_nodes + node) * kWideD + d] = v / fmaxf(nrm, 1e-12f);
+}
+
+template <bool kFp16>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&x)[8]) {
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (kFp16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
+      x[2 * i] = f.x; x[2 * i + 1] = f.y;
+    } else {
+      x[2 * i] = bf16_lo(u[i]); x[2 * i + 1] = bf16_hi(u[i]);
+    }
+  }
+}
+
+// One CTA per chunk of up to kChunkRows rows of one node: lane l of every warp owns elements 8l .. 8l+7 of a row.
+template <bool kFp16>
+__global__ void __launch_bounds__(256) pddp_wide_matvec_kernel(PddpParams p, int lv, const int* perm_in, const float* wdir,
+                                                               float* wpart) {
+  __shared__ float acc_w[8][kWideD];
+  __shared__ float acc_s[8][kWideD];
+  __shared__ float acc_t[8];
+  const LevelTables T = level_tables(p.tables, lv, p.table_stride);
+  const int item = blockIdx.x, bh = blockIdx.y;
+  const int node = T.item_node[item], row0 = T.item_row0[item];
+  const int rows = min(kChunkRows, T.node_size[node] - row0);
+  const int start = T.node_start[node] + row0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool live = lane * 8 < p.D;
+  float v[8], w[8], sx[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[j] = live ? wdir[((size_t)bh * p.dir_nodes + node) * kWideD + lane * 8 + j] : 0.f;
+    w[j] = 0.f; sx[j] = 0.f;
+  }
+  float st = 0.f;
+  const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x) + 2 * (size_t)bh * p.x_stride_bh + lane * 16;
+  constexpr int kIn = 4;                                         // rows in flight per warp
+#pragma unroll 1
+  for (int r = warp * kIn; r < rows; r += 8 * kIn) {
+    uint4 raw[kIn];
+#pragma unroll
+    for (int i = 0; i < kIn; ++i) {
+      raw[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (r + i < rows && live) {
+        const int id = perm_in[(size_t)bh * p.N + start + r + i];
+        raw[i] = *reinterpret_cast<const uint4*>(xb + 2 * (size_t)id * p.x_stride_row);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kIn; ++i) {
+      float x[8];
+      unpack8<kFp16>(raw[i], x);
+      float t = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t = fmaf(x[j], v[j], t);
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { w[j] = fmaf(x[j], t, w[j]); sx[j] += x[j]; }
+      st += t;                                                   // (rows beyond the chunk are zero rows: t = 0)
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { acc_w[warp][lane * 8 + j] = w[j]; acc_s[warp][lane * 8 + j] = sx[j]; }
+  if (lane == 0) acc_t[warp] = st;
+  __syncthreads();
+  float* out = wpart + ((size_t)bh * p.max_items + item) * kWideFloats;
+  const int d = threadIdx.x;
+  float a = 0.f, b = 0.f;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) { a += acc_w[q][d]; b += acc_s[q][d]; }          // warps in fixed order
+  out[d] = a;
+  out[kWideD + d] = b;
+  if (d == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += acc_t[q];
+    out[2 * kWideD] = t;
+  }
+}
+
+// next vector of every node: chunks combined in order, centred, normalised
+__global__ void __launch_bounds__(256) pddp_wide_step_kernel(PddpParams p, int lv, float* wdir, const float* wpart) {
+  __shared__ float red[8];
+  const LevelTables T = level_tables(p.tables, lv, p.table_stride);
+  const int node = blockIdx.x, bh = blockIdx.y, d = threadIdx.x;
+  const int size = T.node_size[node];
+  const int item0 = T.node_item0[node];
+  const int n_items = (size + kChunkRows - 1) / kChunkRows;
+  const float* part = wpart + ((size_t)bh * p.max_items + item0) * kWideFloats;
+  float wr = 0.f, s = 0.f, t = 0.f;
+  for (int it = 0; it < n_items; ++it) {
+    wr += part[(size_t)it * kWideFloats + d];
+    s += part[(size_t)it * kWideFloats + kWideD + d];
+    t += part[(size_t)it * kWideFloats + 2 * kWideD];
+  }
+  float v = wr - s * (t / (float)size);
+  const float nrm = sqrtf(block_sum_256(v * v, red));
+  wdir[((size_t)bh * p.dir_nodes + node) * kWideD + d] = v / fmaxf(nrm, 1e-12f);
+}
+
+// projection of every row on its node's direction, eight elements per lane (the counterpart of pddp_project_kernel)
+template <bool kFp16>
+__global__ void __launch_bounds__(256) pddp_wide_project_kernel(PddpParams p, int lv, int nodes, int pad, const int* perm_in,
+                                                                const float* wdir, float* proj_out) {
+  const LevelTables T = level_tables(p.tables, lv, p.table_stride);
+  const int bh = blockIdx.y;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)nodes * pad;
+  const long long slot0 = warp * kProjRows;
+  if (slot0 >= total) return;
+  const int node = (int)(slot0 / pad), r0 = (int)(slot0 % pad);
+  unsigned long long* keys = p.keys + (size_t)bh * p.key_stride;
+  const int nsize = T.node_size[node];
+  const int pos0 = T.node_start[node] + r0;
+  const bool live = lane * 8 < p.D;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = live ? wdir[((size_t)bh * p.dir_nodes + node) * kWideD + lane * 8 + j] : 0.f;
+  int my_id = -1;
+  if (lane < kProjRows && r0 + lane < nsize) my_id = perm_in[(size_t)bh * p.N + pos0 + lane];
+  uint4 raw[kProjRows];
+#pragma unroll
+  for (int i = 0; i < kProjRows; ++i) {
+    const int id = __shfl_sync(0xffffffffu, my_id, i);
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (id >= 0 && live)
+      raw[i] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.x) +
+                                              2 * ((size_t)bh * p.x_stride_bh + (size_t)id * p.x_stride_row) + lane * 16);
+  }
+#pragma unroll
+  for (int i = 0; i < kProjRows; ++i) {
+    float x[8];
+    unpack8<kFp16>(raw[i], x);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(x[j], v[j], acc);
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const int r = r0 + i;
+      if (r >= nsize) {
+        keys[slot0 + i] = 0xFFFFFFFFFFFFFFFFull;
+      } else {
+        keys[slot0 + i] = ((unsigned long long)float_key(acc) << 32) | (unsigned)r;
+        if (proj_out != nullptr) proj_out[(size_t)bh * p.N + pos0 + i] = acc;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // sort: bitonic network over segments of `pad` keys (power of two), ascending inside each segment
 // ------------------------------------------------------------------------------------------
@@ -521,18 +704,38 @@ int launch_pddp(const PddpArgs& a, cudaStream_t stream) {
     const int power_smem = (128 * 128 + 128 + 512 + 8) * sizeof(float);
     if (cudaFuncSetAttribute(pddp_power_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, power_smem) != cudaSuccess) return -8;
     const float* v0 = a.start_vectors;
+    const bool wide = a.D != 64 && a.D != 128;
+    // wide path: per-chunk partial sums first, then the directions (256 floats per node), both inside the partial area
+    float* wpart = p.partial;
+    float* wdir = p.partial + (size_t)BH * p.max_items * kWideFloats;
+    if (wide && ((size_t)BH * p.max_items * kWideFloats + (size_t)BH * pl.K * kWideD) >
+                    (size_t)BH * p.max_items * kPartialFloats)
+      return -7;
     for (int lv = 0; lv < pl.levels; ++lv) {
       const LevelShape& ls = pl.shape[lv];
       if (a.perm_levels != nullptr)
         cudaMemcpyAsync(a.perm_levels + (size_t)lv * total, perm_a, total * sizeof(int), cudaMemcpyDeviceToDevice, stream);
-      gram<<<dim3(ls.items, BH), kGramThreads, kGramSmem, stream>>>(p, lv, perm_a);
-      pddp_power_kernel<<<dim3(ls.nodes, BH), 512, power_smem, stream>>>(p, lv, ls.nodes, v0);
-      v0 += (size_t)BH * ls.nodes * a.D;
       const long long slots = (long long)ls.nodes * ls.pad;
       float* proj = a.proj_levels != nullptr ? a.proj_levels + (size_t)lv * total : nullptr;
       const unsigned pgrid = (unsigned)((slots / kProjRows * 32 + 255) / 256);
-      if (a.fp16) pddp_project_kernel<true><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
-      else pddp_project_kernel<false><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
+      if (wide) {
+        // Gram-free power iterations (head dimensions other than 64 / 128); partial sums and directions live in the
+        // area the Gram partials would use
+        pddp_wide_init_kernel<<<dim3(ls.nodes, BH), 256, 0, stream>>>(p, ls.nodes, v0, wdir);
+        for (int it = 0; it < a.pow_iters; ++it) {
+          if (a.fp16) pddp_wide_matvec_kernel<true><<<dim3(ls.items, BH), 256, 0, stream>>>(p, lv, perm_a, wdir, wpart);
+          else pddp_wide_matvec_kernel<false><<<dim3(ls.items, BH), 256, 0, stream>>>(p, lv, perm_a, wdir, wpart);
+          pddp_wide_step_kernel<<<dim3(ls.nodes, BH), 256, 0, stream>>>(p, lv, wdir, wpart);
+        }
+        if (a.fp16) pddp_wide_project_kernel<true><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, wdir, proj);
+        else pddp_wide_project_kernel<false><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, wdir, proj);
+      } else {
+        gram<<<dim3(ls.items, BH), kGramThreads, kGramSmem, stream>>>(p, lv, perm_a);
+        pddp_power_kernel<<<dim3(ls.nodes, BH), 512, power_smem, stream>>>(p, lv, ls.nodes, v0);
+        if (a.fp16) pddp_project_kernel<true><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
+        else pddp_project_kernel<false><<<dim3(pgrid, BH), 256, 0, stream>>>(p, lv, ls.nodes, ls.pad, perm_a, proj);
+      }
+      v0 += (size_t)BH * ls.nodes * a.D;
       // bitonic sort of every segment of `pad` keys
       const int tile = std::min(ls.pad, kSortTile);
       const unsigned tiles = (unsigned)(slots / tile);

@@ -29,7 +29,8 @@ from typing import Callable, Optional, Sequence
 
 BLKQ = 128
 TILE_N = 128
-SUPPORTED_HEAD_DIMS = (64, 128)
+# the reference's dispatch lists (128, 144); here every stage also exists for the other sizes of its kernel table and for 64
+SUPPORTED_HEAD_DIMS = (64, 96, 128, 144, 160, 192, 256)
 DEFAULT_TOPK = 0.25
 DEFAULT_NUM_STEPS = 50
 DEFAULT_DENSE_STEPS = 10

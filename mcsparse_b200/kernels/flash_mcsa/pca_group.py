@@ -60,7 +60,8 @@ def pca_group_perm(x: Tensor, C: int = 128, pow_iters: int = 4, seed: int = 0, p
                    *, start_vectors: Optional[Tensor] = None, return_debug: bool = False):
     """Per-head permutation from recursive principal-direction bisection.
 
-    x: (BH, N, D) bf16/fp16 CUDA tensor with contiguous rows (any batch/row strides), D in {64, 128}.
+    x: (BH, N, D) bf16/fp16 CUDA tensor with contiguous rows (any batch/row strides), D a multiple of 8 up to 256
+    (64 and 128 on the tensor-core Gram path, the others on Gram-free power iterations).
     Returns perm (BH, N) int64: ``x[b, perm[b, i]]`` is the i-th reordered token.  ``proj_dim`` (an
     option the reference leaves off by default) is not part of this path.  ``return_debug`` adds the
     per-level fp32 projections (levels, BH, N) and orders (levels + 1, BH, N).
@@ -76,8 +77,8 @@ def pca_group_perm(x: Tensor, C: int = 128, pow_iters: int = 4, seed: int = 0, p
         return identity_perm(BH, N, x.device)
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError(f"x must be bf16 or fp16, got {x.dtype}")
-    if D not in (64, 128):
-        raise ValueError(f"head_dim must be 64 or 128, got {D}")
+    if D % 8 != 0 or not (8 <= D <= 256):
+        raise ValueError(f"head_dim must be a multiple of 8 up to 256, got {D}")
     if x.stride(-1) != 1:
         x = x.contiguous()
     L = _lib.lib()

@@ -19,10 +19,12 @@ def _qkv(B, H, L, D, seed):
     return mk(), mk(), torch.randn(B, H, L, D, generator=g).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("pca", [False, True])
-def test_calibrate_then_reuse(cuda_device, pca):
+# D = 144 is the second head dimension of the reference's dispatch (token_sparse_dispatch.py:121): every stage of the
+# state machine runs on the padded-layout kernels there
+@pytest.mark.parametrize("pca,D", [(False, 128), (True, 128), (True, 144), (False, 144), (True, 64), (True, 256)])
+def test_calibrate_then_reuse(cuda_device, pca, D):
     from mcsparse_b200.kernels.flash_mcsa.token_sparse import TokenSparseConfig, TokenSparseContext
-    B, H, L, D = 1, 2, 1500, 128
+    B, H, L = 1, 2, 1500
     cfg = TokenSparseConfig(topk=0.25, calibrate_steps=[0], sink_ranges=[(0, 4)], bias_correction=True, pca_reorder=pca,
                             pca_pow_iters=4)
     ctx = TokenSparseContext(cfg, num_layers=1)

@@ -130,7 +130,7 @@ def test_dispatch_counters_and_layer_clock():
     assert d(long_, long_, long_, attn_mask=object()) == "dense"
     assert d(long_, long_, long_, is_causal=True) == "dense"
     assert d(FakeTensor((1, 2048, 2, 128), cuda=False), long_, long_) == "dense"
-    assert d(FakeTensor((1, 2048, 2, 96)), FakeTensor((1, 2048, 2, 96)), FakeTensor((1, 2048, 2, 96))) == "dense"
+    assert d(FakeTensor((1, 2048, 2, 100)), FakeTensor((1, 2048, 2, 100)), FakeTensor((1, 2048, 2, 100))) == "dense"
     assert tsd.get_mcsa_token_stats()["fallback_calls"] == 10
 
 
@@ -181,7 +181,7 @@ def test_eligibility_table():
     assert tsd.check_eligibility(**base) == (True, "", "")
     for change in (dict(has_parallel_config=True), dict(has_attn_mask=True), dict(is_causal=True), dict(dropout_p=0.1),
                    dict(enable_gqa=True), dict(ndim=3), dict(is_cuda=False), dict(dtype_ok=False), dict(shapes_match=False),
-                   dict(seq_len_k=4096), dict(head_dim=96), dict(seq_len_q=301, seq_len_k=301), dict(sparse_seq_len=16384)):
+                   dict(seq_len_k=4096), dict(head_dim=100), dict(seq_len_q=301, seq_len_k=301), dict(sparse_seq_len=16384)):
         ok, reason, severity = tsd.check_eligibility(**{**base, **change})
         assert not ok and reason and severity == "fallback", change
     ok, _, severity = tsd.check_eligibility(**{**base, "sink_tokens": 8192})

@@ -18,8 +18,10 @@ def _clustered(BH, N, D, seed):
     return (cent[:, cid] + 0.3 * torch.randn(BH, N, D, generator=g)).to(torch.bfloat16)
 
 
+# (the head dimensions other than 64 and 128 run Gram-free power iterations; the contract is the same)
 @pytest.mark.parametrize("BH,N,D,C,iters", [(2, 1000, 128, 128, 8), (2, 2048, 64, 128, 4), (1, 5000, 128, 128, 8),
-                                            (1, 9000, 128, 64, 4)])
+                                            (1, 9000, 128, 64, 4), (2, 5000, 144, 128, 8), (1, 3000, 256, 128, 4),
+                                            (2, 2500, 96, 128, 8), (1, 1000, 160, 64, 0)])
 def test_two_stage_contract(cuda_device, BH, N, D, C, iters):
     from mcsparse_b200.kernels.flash_mcsa.pca_group import pca_group_perm, pddp_start_vectors
     x = _clustered(BH, N, D, N)
