@@ -224,7 +224,7 @@ typedef struct mcs_group_mass_args {
   int32_t* status;
   int64_t q_stride[3];
   int64_t k_stride[3];
-  int32_t B, H, Lq, Lk, D;
+  int32_t B, H, Lq, Lk, D;   /* D: a multiple of 8 up to 256 (64 and 128 on the tuned tile layouts) */
   int32_t group_rows;   /* 1..128 */
   int32_t dtype;        /* MCS_DTYPE_BF16 or MCS_DTYPE_FP16 */
   int32_t normalize;    /* 0: sum, 1: divide by rows in group */
@@ -308,7 +308,7 @@ typedef struct mcs_pddp_args {
   int32_t* status;
   int64_t x_stride_bh, x_stride_row;
   int64_t workspace_bytes;
-  int32_t BH, N, D, C, pow_iters;
+  int32_t BH, N, D, C, pow_iters;   /* D: a multiple of 8 up to 256 (64 and 128 through the tensor-core Gram matrix) */
   int32_t dtype;         /* MCS_DTYPE_BF16 or MCS_DTYPE_FP16 */
 } mcs_pddp_args;
 
