@@ -765,6 +765,10 @@ def run_anchor(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     shape = synth.C2
+    if args.head_dim:
+        # the same grid at another head dimension (those other than 64 / 128 run on the padded-layout kernels)
+        import dataclasses
+        shape = dataclasses.replace(shape, head_dim=args.head_dim, name=shape.name + f"_D{args.head_dim}")
     H = args.heads or shape.heads
     L, D = shape.seq_len, shape.head_dim
     q, k, _ = synth.clustered_qkv(shape, heads=H, device=dev)
