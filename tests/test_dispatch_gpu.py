@@ -74,3 +74,31 @@ def test_dispatch_schedule_end_to_end(cuda_device, D):
     assert mx < 2e-2 and mr < 1e-2, (mx, mr)
     tsd.reset_mcsa_token_state()
     assert tsd.get_mcsa_token_stats()["dispatch_calls"] == 0
+
+
+def test_ulysses_wrapper_without_context_parallelism_runs_the_local_kernel(cuda_device):
+    """``with_ulysses_sparse`` with no parallel configuration is the plain token-sparse dispatch (reference
+    context_parallel.py:201-209): ``local_calls`` counts, the original dispatch only sees what the inner dispatch
+    hands it."""
+    from mcsparse_b200.h3 import context_parallel as cp, token_sparse_dispatch as tsd
+    dev = cuda_device
+    B, T, H, D = 1, 1536, 2, 128
+
+    def original(q, k, v, *a, **kw):
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2).float(), k.transpose(1, 2).float(),
+                                                             v.transpose(1, 2).float())
+        return o.transpose(1, 2).to(q.dtype).contiguous()
+
+    cp.reset_cp_stats()
+    d = cp.with_ulysses_sparse(original, kind="mcsa_token", sink_tokens=0, allow_no_sink=True, num_layers=1, topk=0.25,
+                               dense_steps=0, dense_layers="", calibrate_steps=(0,), min_seq_len=1024)
+    q, k, v = _qkv(B, T, H, D, 3)
+    dense, _ = dense_attn_ref(q, k, v)
+    for step in range(2):                                  # anchor step, then a reuse step on the same tensors
+        tsd.mcsa_token_begin_forward()
+        out = d(q.to(dev), k.to(dev), v.to(dev))
+        mx, mr = error_metrics(out.float().cpu(), dense)
+        assert mx < 3e-2 and mr < 1.5e-2, (step, mx, mr)
+    st = cp.get_cp_stats()
+    assert st["local_calls"] == 2 and st["cp_calls"] == 0
+    assert tsd.get_mcsa_token_stats()["kernel_calls"] == 2
