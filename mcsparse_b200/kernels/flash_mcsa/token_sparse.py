@@ -379,6 +379,9 @@ class TokenSparseConfig:
         if self.cache_offload == 'residual':
             assert self.bias_correction, "cache_offload='residual' requires bias_correction=True"
         assert not (self.compact_indices and self.offload_indices), "compact_indices keeps the indices in HBM; choose one of the two"
+        if self.share_lse:
+            raise NotImplementedError("share_lse (one layer's LSE reused by the others) is not part of the accelerated path: "
+                                      "every layer computes its own")
 
 
 # modes in which the permutation is renewed together with the selection (token_sparse.py:984); an update

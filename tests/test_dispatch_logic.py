@@ -43,6 +43,8 @@ def test_config_guards():
         TokenSparseConfig(cal_downsample=2)
     with pytest.raises(NotImplementedError):
         TokenSparseConfig(pca_proj_dim=32)
+    with pytest.raises(NotImplementedError):
+        TokenSparseConfig(share_lse=True)                             # accepted by the reference, not built here: say so
 
 
 def test_residual_dropped_when_permutation_is_newer():
